@@ -1,4 +1,4 @@
-from . import attention, block, embedding, feed_forward, head, latent_attention, mingru, norm, position, streams, wkv  # noqa: F401  (register the built-in kinds)
+from . import attention, block, embedding, feed_forward, head, junction, latent_attention, mingru, norm, parallel, position, retention, streams, wkv  # noqa: F401  (register the built-in kinds)
 from .base import (Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, build_part, register_block,
                    register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
                    register_position)

@@ -96,8 +96,13 @@ class GatedAttentionMixer(Mixer):
     ``qk_norm``: queries and keys are then divided by their root mean square over the head (eps inside the root).
     ``mask``: "full" (every earlier key), "window" (the last ``mask_size`` keys) or "chunk" (the earlier keys of the
     query's own chunk of ``mask_size`` positions, counted from position 0 of the sequence).
+    ``norm_weights``: the unit norm becomes an RMS norm with a weight of ``dim`` numbers, one for the queries and one for
+    the keys, shared by their heads.
+    ``temp_coef``, ``temp_every``: a query temperature: the query at position p is multiplied (after its norm) by
+    1 + temp_coef * ln(floor((p + 1) / temp_every) + 1); 0 for none.
     ``sink``: 1 is added to the softmax's denominator, as if every query also saw a key of score 0 and value 0.
-    Every head's output is multiplied by sigmoid(w_g,h . x), x the rows the projections read.  The value size may differ
+    ``gate`` "head": every head's output is multiplied by sigmoid(w_g,h . x), x the rows the projections read; "element":
+    every entry of the concatenated heads by the sigmoid of its own projection of x (``heads * vdim`` gate rows).  The value size may differ
     from the query/key size: the cache and the attention kernels run at ``head`` = the larger, in steps of 16, the
     smaller padded with zeros (scores and outputs are the same).  No biases.
 
@@ -105,10 +110,12 @@ class GatedAttentionMixer(Mixer):
     angles, norms, scores and softmax are float32."""
 
     MASKS = ("full", "window", "chunk")
+    GATES = ("head", "element")
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, rot_base: float = 10000.0,
                  rot_dims: int = 0, conv: int = 0, qk_norm: bool = False, eps: float = 1e-6, mask: str = "full", mask_size: int = 0,
-                 sink: bool = False, conv_group: int = -1, conv_slot: int = -1):
+                 sink: bool = False, conv_group: int = -1, conv_slot: int = -1, norm_weights: bool = False, temp_coef: float = 0.0,
+                 temp_every: int = 1, gate: str = "head"):
         if heads % kv_heads:
             raise ValueError("Invalid GQA head ratio")
         if mask not in self.MASKS or (mask != "full" and mask_size <= 0):
@@ -119,6 +126,14 @@ class GatedAttentionMixer(Mixer):
         self.scale, self.rot_base, self.rot_dims, self.conv = float(scale), float(rot_base), int(rot_dims), int(conv)
         self.qk_norm, self.eps, self.mask, self.mask_size, self.sink = bool(qk_norm), float(eps), mask, int(mask_size), bool(sink)
         self.conv_group, self.conv_slot = int(conv_group), int(conv_slot)
+        self.norm_weights, self.temp_coef, self.temp_every, self.gate = bool(norm_weights), float(temp_coef), int(temp_every), gate
+        if gate not in self.GATES:
+            raise ValueError(f"gate {gate!r}: known gates are {', '.join(self.GATES)}")
+        if self.norm_weights and not self.qk_norm:
+            raise ValueError("norm weights need the query/key norm")
+        if self.temp_every < 1:
+            raise ValueError("temp_every must be positive")
+        self.q_norm_weight = self.k_norm_weight = None
         if self.conv > 1 and self.conv_group < 0:
             raise ValueError("a convolution of more than one tap needs a state slot for its history")
         self.head = -(-max(self.dim, self.vdim) // 16) * 16
@@ -132,11 +147,28 @@ class GatedAttentionMixer(Mixer):
     def channels(self) -> int:
         return (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim
 
+    @property
+    def gate_width(self) -> int:
+        return self.heads if self.gate == "head" else self.heads * self.vdim
+
+    @property
+    def input_width(self) -> int:
+        """Rows of the one matrix that holds all projections of the mixer's input."""
+        return self.channels + self.gate_width
+
+    @property
+    def inner_width(self) -> int:
+        """Columns of the output projection."""
+        return self.heads * self.vdim
+
     def parameter_shapes(self) -> dict:
-        shapes = {"qkvg.weight": ((self.channels + self.heads, self.hidden_size), "matrix"),
-                  "o.weight": ((self.hidden_size, self.heads * self.vdim), "matrix")}
+        shapes = {"qkvg.weight": ((self.input_width, self.hidden_size), "matrix"),
+                  "o.weight": ((self.hidden_size, self.inner_width), "matrix")}
         if self.conv > 0:
             shapes["conv.weight"] = ((self.channels, self.conv), "vector")
+        if self.norm_weights:
+            shapes["q_norm.weight"] = ((self.dim,), "vector")
+            shapes["k_norm.weight"] = ((self.dim,), "vector")
         return shapes
 
     def bind(self, tensors: dict) -> None:
@@ -159,22 +191,35 @@ class GatedAttentionMixer(Mixer):
         return self._inv_freq[key]
 
     def forward(self, ctx, h, entry):
+        projected = ctx.ops.linear(h, self.qkvg_weight)                      # [T, channels + gates]
+        return ctx.ops.linear(self.mix(ctx, projected, entry), self.o_weight)
+
+    def mix(self, ctx, projected, entry, out=None, scale=1.0):
+        """Everything between the input projections and the output projection: ``projected`` [T, >= input_width] (any
+        row stride) -> the gated heads [T, inner_width], times ``scale``, into ``out`` where given (a view of a wider
+        buffer: a mixer that stands beside another one shares its products with it)."""
         ops = ctx.ops
         group = ctx.groups[entry.cache_group]
         k_cache, v_cache = group.kv_slot(entry.cache_slot)
         slot_mapping = group.slot_mapping if entry.write_cache else None
         history = ctx.groups[self.conv_group].state(self.conv_slot) if self.conv > 1 else None
-        projected = ops.linear(h, self.qkvg_weight)                          # [T, channels + heads]
+        more = {}
+        if self.norm_weights:
+            more.update(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight)
+        if self.temp_coef != 0.0:
+            more.update(temp=(self.temp_coef, self.temp_every))
         queries = ops.qkv_conv_rope_norm_cache(
             projected, self._conv_by_tap, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
-            self.inverse_frequencies(h.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
-            k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size)
+            self.inverse_frequencies(projected.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
+            k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size, **more)
         # one int says what a query sees: 0 every earlier key, w > 0 the last w, -c < 0 its own chunk of c positions
         visibility = {"full": 0, "window": self.mask_size, "chunk": -self.mask_size}[self.mask]
         mixed = ops.paged_attention(queries, k_cache, v_cache, group.block_table, ctx, self.heads, self.kv_heads, self.head,
                                     group.page_size, self.scale, visibility, sink=self.sink)
-        gated = ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim)
-        return ops.linear(gated, self.o_weight)
+        if self.gate == "head" and out is None and scale == 1.0:
+            return ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim)
+        return ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim, per_element=self.gate == "element",
+                             scale=scale, out=out)
 
 
 register_mixer("attention", AttentionMixer)

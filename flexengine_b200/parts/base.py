@@ -43,13 +43,16 @@ Embedding:       ``forward(ctx) -> residual``: the float32 residual stream [T, h
                  tokens (``ctx.token_ids``), which the blocks then add to in place.
 Head:            ``forward(ctx, h) -> logits``: float32 [rows, vocab] from the final norm's output
                  rows (the rows whose logits are wanted, nothing else reaches it).
+Junction:        ``forward(ctx, residual, pending, origin) -> residual``: rewrites the residual stream between two
+                 layers (what the block before left ``pending`` is settled first); ``origin`` is the embedding's
+                 output of this step, untouched.  A run entry names the junction that runs before its layer.
 """
 from __future__ import annotations
 
 from typing import Callable
 
 _REGISTRIES: dict[str, dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "junction": {},
 }
 
 
@@ -83,6 +86,10 @@ def register_embedding(kind: str, factory: Callable) -> None:
 
 def register_head(kind: str, factory: Callable) -> None:
     _register("head", kind, factory)
+
+
+def register_junction(kind: str, factory: Callable) -> None:
+    _register("junction", kind, factory)
 
 
 def build_part(family: str, spec):
@@ -156,6 +163,11 @@ class Embedding(Part):
 
 class Head(Part):
     def forward(self, ctx, h):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Junction(Part):
+    def forward(self, ctx, residual, pending, origin):  # pragma: no cover - interface
         raise NotImplementedError
 
 

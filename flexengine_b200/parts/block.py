@@ -215,6 +215,44 @@ class HyperGatedBlock:
         return StreamUpdate(y, gate, self.rg2.bias, self.hc2.mix, self.hc2.write)
 
 
+class SandwichBlock:
+    """Norms on both sides of every sublayer:
+        x <- x + norm1b(mixer(norm1(x)));  x <- x + norm2b(feed_forward(norm2(x)))   (the second where the layer has one).
+    A sublayer's output is not normed and added at once: it is handed on as ``pending`` (``PostNormed``), and the kernel
+    of the norm that reads the stream next norms it, adds it and norms the sum (the next sublayer's, the next layer's,
+    a junction's, or the model's final norm)."""
+
+    def __init__(self, layer_spec):
+        self.norm1 = build_part("norm", layer_spec.norm)
+        self.norm1b = build_part("norm", layer_spec.norm)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward) if layer_spec.feed_forward is not None else None
+        self.part_names = ("norm1", "mixer", "norm1b")
+        if self.feed_forward is not None:
+            self.norm2 = build_part("norm", layer_spec.norm)
+            self.norm2b = build_part("norm", layer_spec.norm)
+            self.part_names += ("norm2", "feed_forward", "norm2b")
+
+    def parts(self) -> dict:
+        return {name: getattr(self, name) for name in self.part_names}
+
+    @staticmethod
+    def _post(norm, out):
+        """A sublayer may return (rows, bias still to add): the norm's kernel adds it."""
+        return norm.after(*out) if isinstance(out, tuple) else norm.after(out)
+
+    def forward(self, ctx, residual, pending, entry):
+        h = self.norm1.forward(ctx, residual, pending)
+        pending = self._post(self.norm1b, self.mixer.forward(ctx, h, entry))
+        if self.feed_forward is None:
+            return pending
+        h = self.norm2.forward(ctx, residual, pending)
+        if _accepts(self.feed_forward.forward, "defer_bias"):
+            return self._post(self.norm2b, self.feed_forward.forward(ctx, h, defer_bias=True))
+        return self._post(self.norm2b, self.feed_forward.forward(ctx, h))
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)
 register_block("hyper_gated", HyperGatedBlock)
 register_block("parallel_depth_average", ParallelDepthAverageBlock)

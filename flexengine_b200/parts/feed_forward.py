@@ -14,23 +14,40 @@ class SwiGLU(FeedForward):
 
     ACTIVATIONS = ("silu", "gelu_tanh")
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"unknown gate activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
         self.activation = activation
+        self.has_bias = bool(bias)
         self.gate_up_weight = None
         self.down_weight = None
+        self.gate_up_bias = self.down_bias = None
+        if self.has_bias:
+            self.takes_prenormed = False
 
     def parameter_shapes(self) -> dict:
         h, i = self.hidden_size, self.intermediate_size
-        return {"gate_up.weight": ((2 * i, h), "matrix"), "down.weight": ((h, i), "matrix")}
+        shapes = {"gate_up.weight": ((2 * i, h), "matrix"), "down.weight": ((h, i), "matrix")}
+        if self.has_bias:
+            shapes.update({"gate_up.bias": ((2 * i,), "vector"), "down.bias": ((h,), "vector")})
+        return shapes
 
     def reads_first(self):
         return self.gate_up_weight
 
-    def forward(self, ctx, h, follow=None, upcoming=None):
+    def forward(self, ctx, h, follow=None, upcoming=None, defer_bias=False):
+        """``defer_bias``: the caller adds the last product's bias itself (a norm's kernel that reads the output next);
+        (rows in float32, bias) come back."""
+        if self.has_bias:
+            ops = ctx.ops
+            # the products stay float32 until their biases are in: one rounding each
+            gate_up = ops.linear(h, self.gate_up_weight, None, out_float32=True)
+            act = ops.gated_activation(gate_up, self.intermediate_size, self.activation, bias=self.gate_up_bias, out_dtype=ctx.dtype)
+            if defer_bias:
+                return ops.linear(act, self.down_weight, None, out_float32=True), self.down_bias
+            return ops.linear(act, self.down_weight, self.down_bias)
         if self.activation != "silu":
             act = ctx.ops.linear_gated(h, self.gate_up_weight, self.intermediate_size, self.activation)
             return ctx.ops.linear(act, self.down_weight)
@@ -70,9 +87,21 @@ class RoutedExperts(FeedForward):
     none) that every token runs.  Tokens are sorted by expert on the device and each expert multiplies its own
     rows (``ops.routed_experts``): no count ever comes back to the host, so the step can be a CUDA graph."""
 
-    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, scale: float = 1.0, shared_size: int = 0):
+    ROUTERS = ("softmax_all", "softmax_chosen")
+    ACTIVATIONS = ("silu", "clamped")
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, scale: float = 1.0, shared_size: int = 0,
+                 router: str = "softmax_all", activation: str = "silu", limit: float = 0.0):
+        """``router`` "softmax_all": as above; "softmax_chosen": the ``top`` largest logits are chosen and the weights are
+        the softmax over the chosen logits only.  ``activation`` "silu": as above; "clamped": with g = min(gate h, limit)
+        and u = clamp(up h, -limit, limit) an expert is down( g * sigmoid(1.702 g) * (u + 1) )."""
         self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
         self.expert_size, self.scale, self.shared_size = int(expert_size), float(scale), int(shared_size)
+        if router not in self.ROUTERS or activation not in self.ACTIVATIONS:
+            raise ValueError(f"router {router!r} / activation {activation!r}: known are {self.ROUTERS} and {self.ACTIVATIONS}")
+        if activation == "clamped" and not limit > 0.0:
+            raise ValueError("the clamped activation needs a positive limit")
+        self.router, self.activation, self.limit = router, activation, float(limit)
         self.router_weight = self.experts_gate_up_weight = self.experts_down_weight = None
         self.shared_gate_up_weight = self.shared_down_weight = None
 
@@ -92,12 +121,15 @@ class RoutedExperts(FeedForward):
         ops = ctx.ops
         e, f, d = self.experts, self.expert_size, self.hidden_size
         logits = ops.linear(h, self.router_weight, None, out_float32=True)
-        chosen, weights = ops.route_top(logits, self.top, self.scale)
         shared = None
         if self.shared_size:
             shared = ops.linear(ops.linear_swiglu(h, self.shared_gate_up_weight, self.shared_size), self.shared_down_weight)
-        return ops.routed_experts(h, chosen, weights, self.experts_gate_up_weight.view(e, 2 * f, d),
-                                  self.experts_down_weight.view(e, d, f), shared)
+        gate_up, down = self.experts_gate_up_weight.view(e, 2 * f, d), self.experts_down_weight.view(e, d, f)
+        if self.router == "softmax_all" and self.activation == "silu":
+            chosen, weights = ops.route_top(logits, self.top, self.scale)
+            return ops.routed_experts(h, chosen, weights, gate_up, down, shared)
+        chosen, weights = ops.route_top(logits, self.top, self.scale, over_chosen=self.router == "softmax_chosen")
+        return ops.routed_experts(h, chosen, weights, gate_up, down, shared, activation=self.activation, limit=self.limit)
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -20,6 +20,7 @@ class DecoderModel:
         sizes = {"vocab_size": plan.vocab_size, "hidden_size": plan.hidden_size}
         self.embedding = build_part("embedding", plan.embedding or PartSpec("token_table", sizes))
         self.head = build_part("head", plan.head or PartSpec("linear", sizes))
+        self.junctions = [build_part("junction", spec) for spec in plan.junctions]
         self.dtype = None
         self.device = None
 
@@ -34,6 +35,9 @@ class DecoderModel:
             for part_name, part in block.parts().items():
                 for name, (shape, kind) in part.parameter_shapes().items():
                     shapes[("layer", i, part_name, name)] = (shape, kind)
+        for j, part in enumerate(self.junctions):
+            for name, (shape, kind) in part.parameter_shapes().items():
+                shapes[("junction", j, name)] = (shape, kind)
         return shapes
 
     def bind(self, tensors: dict, dtype, device) -> None:
@@ -45,6 +49,8 @@ class DecoderModel:
             for part_name, part in block.parts().items():
                 part.bind({k[3]: t for k, t in tensors.items()
                            if k[0] == "layer" and k[1] == i and k[2] == part_name})
+        for j, part in enumerate(self.junctions):
+            part.bind({k[2]: t for k, t in tensors.items() if k[0] == "junction" and k[1] == j})
 
     def _outer_parts(self):
         """The parts outside the layers, under the names their bindings use."""
@@ -62,7 +68,7 @@ class DecoderModel:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-        for part in [p for _, p in self._outer_parts()] + [p for b in self.blocks for p in b.parts().values()]:
+        for part in [p for _, p in self._outer_parts()] + [p for b in self.blocks for p in b.parts().values()] + self.junctions:
             for name in part.parameter_shapes():
                 visit(getattr(part, name.replace(".", "_"), None))
         return total
@@ -82,8 +88,12 @@ class DecoderModel:
         residual = self.embedding.forward(ctx)
         pending = None
         run = self.plan.run
+        # a junction may read the embedding's output, which the blocks add to in place: it gets a copy
+        origin = residual.clone() if self.junctions else None
         for at, entry in enumerate(run):
             block = self.blocks[entry.layer]
+            if entry.before >= 0:
+                residual, pending = self.junctions[entry.before].forward(ctx, residual, pending, origin), None
             # a block that can make use of it is told which norm reads the residual after it
             after = self.blocks[run[at + 1].layer] if at + 1 < len(run) else None
             if after is not None and getattr(after, "takes_prenormed", False) and self._knows_next_norm(block):

@@ -12,6 +12,17 @@ import torch
 from .base import Norm, register_norm
 
 
+class PostNormed:
+    """A branch's output on its way into the residual stream through a norm of its own: the stream receives
+    w * (y + bias) / sqrt(mean((y + bias)^2) + eps).  The kernel of the norm that reads the stream next does it (the
+    ``pending`` of this framework: a branch output is not added at once).  ``y`` is float32 or in the compute dtype,
+    ``bias`` (float32, may be None) what the branch's last product has yet to add."""
+    __slots__ = ("y", "weight", "eps", "bias")
+
+    def __init__(self, y, weight, eps, bias=None):
+        self.y, self.weight, self.eps, self.bias = y, weight, float(eps), bias
+
+
 class RMSNorm(Norm):
     def __init__(self, hidden_size: int, eps: float):
         self.hidden_size = int(hidden_size)
@@ -22,7 +33,16 @@ class RMSNorm(Norm):
         return {"weight": ((self.hidden_size,), "vector")}
 
     def forward(self, ctx, residual, delta, rows=None, upcoming=None):
+        if isinstance(delta, PostNormed):
+            # the branch before ends in a norm of its own (a layer with norms on both sides of a sublayer): one kernel
+            # norms the branch's output, adds it to the stream and norms the sum
+            return ctx.ops.add_rmsnorm(residual, delta.y, self.weight, self.eps, ctx.dtype, rows,
+                                       post=(delta.weight, delta.eps, delta.bias))
         return ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype, rows, upcoming=upcoming)
+
+    def after(self, y, bias=None) -> PostNormed:
+        """``y`` on its way through this norm into the residual stream (this norm follows a sublayer)."""
+        return PostNormed(y, self.weight, self.eps, bias)
 
     def following(self, ctx, residual):
         # a decode step in bfloat16 on kernels that can: the product before this norm adds to the residual and

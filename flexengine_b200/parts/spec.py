@@ -82,11 +82,24 @@ class RunEntry:
     ``layer`` indexes ``ModelPlan.layers`` (the same layer may appear more than once).
     ``cache_group``/``cache_slot`` say where this run's mixer keeps what it remembers;
     ``write_cache=False`` makes it read what another entry wrote into that slot.
+    ``more``: further (cache group, cache slot) pairs of this run, for a mixer that keeps more than one thing (two
+    mixers side by side: the first takes ``cache_group``/``cache_slot``, the others one pair each, in their order).
+    ``before``: the junction (an index into ``ModelPlan.junctions``) that rewrites the residual stream right before this
+    run's layer; -1 for none.
     """
     layer: int
     cache_group: int = 0
     cache_slot: int = 0
     write_cache: bool = True
+    more: tuple = ()
+    before: int = -1
+
+    def place(self, index: int) -> "RunEntry":
+        """The entry as mixer ``index`` of several side by side sees it: its own cache group and slot."""
+        if index == 0:
+            return self
+        group, slot = self.more[index - 1]
+        return RunEntry(self.layer, group, slot, self.write_cache)
 
 
 @dataclass(frozen=True)
@@ -100,8 +113,8 @@ class WeightSource:
 class WeightBinding:
     """Where checkpoint tensors go.
 
-    ``target`` is ("embedding"|"final_norm"|"lm_head", local) or ("layer", i, part, local)
-    with part in {"mixer", "feed_forward", "norm"}.  Several sources are concatenated
+    ``target`` is ("embedding"|"final_norm"|"lm_head", local), ("layer", i, part, local)
+    with part in {"mixer", "feed_forward", "norm"}, or ("junction", j, local).  Several sources are concatenated
     along dim 0 in the given order.  ``alias_of`` binds the target to another target's
     storage instead (tied embeddings); then ``sources`` is empty, and ``absent`` may name
     checkpoint tensors whose presence contradicts the alias (``why`` says what they contradict).
@@ -136,6 +149,10 @@ class ModelPlan:
     bos_token_id: int | None = None
     # statistics of random initialisation, by binding kind / local name
     init: Mapping[str, Any] = field(default_factory=dict)
+    # parts that rewrite the residual stream between layers (a run entry names one with ``before``)
+    junctions: Sequence[PartSpec] = ()
+    # checkpoint tensors that may be present although nothing of the plan reads them
+    ignored: tuple = ()
 
     def validate(self) -> None:
         for e in self.run:
@@ -146,6 +163,11 @@ class ModelPlan:
             g = self.cache_groups[e.cache_group]
             if not (0 <= e.cache_slot < g.slots):
                 raise ValueError(f"run entry names slot {e.cache_slot} of group {g.name!r} with {g.slots} slots")
+            for group, slot in e.more:
+                if not (0 <= group < len(self.cache_groups)) or not (0 <= slot < self.cache_groups[group].slots):
+                    raise ValueError(f"run entry names slot {slot} of cache group {group}, which the plan does not have")
+            if not (-1 <= e.before < len(self.junctions)):
+                raise ValueError(f"run entry names junction {e.before}, plan has {len(self.junctions)}")
         written = {(e.cache_group, e.cache_slot) for e in self.run if e.write_cache}
         for e in self.run:
             if not e.write_cache and (e.cache_group, e.cache_slot) not in written:

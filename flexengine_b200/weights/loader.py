@@ -51,7 +51,7 @@ def check_against_plan(plan, entries: dict) -> None:
             wanted[s.name] = tuple(s.shape)
             kinds[s.name] = b.kind
     missing = sorted(set(wanted) - set(entries), key=_natural)
-    unexpected = sorted(set(entries) - set(wanted), key=_natural)
+    unexpected = sorted(set(entries) - set(wanted) - set(plan.ignored), key=_natural)
     wrong_shape, wrong_dtype = [], []
     for name in sorted(set(wanted) & set(entries), key=_natural):
         e = entries[name]

@@ -22,7 +22,23 @@ def carry_tokens(token_ids, rows, sources, previous):
     token_ids[rows[keep].long()] = previous[sources[keep].long()].to(token_ids.dtype)
 
 
-def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None):
+def _post_normed(delta, post):
+    """What a branch output becomes on its way through a norm of its own: w * (y + bias) / rms(y + bias)."""
+    weight, eps, bias = post
+    y = delta.float() if bias is None else delta.float() + bias.float()
+    return y * torch.rsqrt(y.pow(2).mean(dim=-1, keepdim=True) + eps) * weight.float()
+
+
+def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None, post=None):
+    if post is not None and delta is not None:
+        delta = _post_normed(delta if rows is None else delta[rows.long()], post)
+        if rows is None:
+            residual += delta
+            x = residual
+        else:
+            x = residual[rows.long()] + delta
+        variance = x.pow(2).mean(dim=-1, keepdim=True)
+        return (x * torch.rsqrt(variance + eps) * weight.float()).to(out_dtype)
     if rows is None:
         if delta is not None:
             residual += delta.float()
@@ -33,6 +49,20 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=Non
             x = x + delta[rows.long()].float()
     variance = x.pow(2).mean(dim=-1, keepdim=True)
     return (x * torch.rsqrt(variance + eps) * weight.float()).to(out_dtype)
+
+
+def residual_concat(residual, delta, extra, out_dtype, post=None):
+    """residual += delta (through its own norm with ``post``), then [residual | extra] in ``out_dtype``."""
+    if delta is not None:
+        residual += _post_normed(delta, post) if post is not None else delta.float()
+    return torch.cat([residual, extra.float()], dim=-1).to(out_dtype)
+
+
+def scale_softcap(logits, scale, cap):
+    logits.mul_(scale)
+    if cap > 0.0:
+        logits.copy_(cap * torch.tanh(logits / cap))
+    return logits
 
 
 def linear(x, w, bias=None, out_float32=False):
@@ -52,16 +82,18 @@ def linear_swiglu(x, w, intermediate):
     return swiglu(linear(x, w), intermediate)
 
 
-def gated_activation(gate_up, intermediate, activation):
+def gated_activation(gate_up, intermediate, activation, bias=None, out_dtype=None):
     g = gate_up[:, :intermediate].float()
     u = gate_up[:, intermediate:].float()
+    if bias is not None:
+        g, u = g + bias[:intermediate].float(), u + bias[intermediate:].float()
     if activation == "silu":
         a = g / (1.0 + torch.exp(-g))
     elif activation == "gelu_tanh":
         a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g * g * g)))
     else:
         raise ValueError(activation)
-    return (a * u).to(gate_up.dtype)
+    return (a * u).to(out_dtype or gate_up.dtype)
 
 
 def linear_gated(x, w, intermediate, activation):
@@ -192,7 +224,8 @@ def token_shift(h, mu, kept, state_slots, cu_q, token_request):
 
 
 def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, token_request, positions, inv_freq, rot_dims,
-                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size,
+                             q_weight=None, k_weight=None, temp=None):
     """projected [T, >= channels] holds q | k | v.  A causal convolution of ``taps`` taps over time per channel (``conv``
     [taps, channels]; ``history`` [seats, (taps - 1) channels] holds every request's last taps - 1 projected rows and is
     brought up to date), rotation of the first ``rot_dims`` entries of the query and key heads, their unit norm, keys and
@@ -228,6 +261,11 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
     if qk_norm:
         q = q * torch.rsqrt(q.pow(2).mean(dim=-1, keepdim=True) + eps)
         k = k * torch.rsqrt(k.pow(2).mean(dim=-1, keepdim=True) + eps)
+    if q_weight is not None:
+        q, k = q * q_weight.float(), k * k_weight.float()
+    if temp is not None:
+        coef, every = temp
+        q = q * (1.0 + coef * torch.log(torch.div(positions + 1, every, rounding_mode="floor").float() + 1.0))[:, None, None]
     dt = projected.dtype
     queries = torch.zeros(T, heads, head, dtype=dt, device=u.device)
     queries[..., :dim] = q.to(dt)
@@ -244,12 +282,56 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
     return queries.view(T, heads * head)
 
 
-def head_gate(mixed, projected, offset, heads, head, vdim):
-    """out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h])."""
+def head_gate(mixed, projected, offset, heads, head, vdim, per_element=False, scale=1.0, out=None):
+    """out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h]) * scale; with ``per_element`` the gate of
+    entry j of head h is projected[t, offset + h vdim + j]."""
     T = mixed.shape[0]
-    gate = torch.sigmoid(projected[:, offset:offset + heads].float())
-    out = mixed.view(T, heads, head)[..., :vdim].float() * gate[:, :, None]
-    return out.reshape(T, heads * vdim).to(mixed.dtype)
+    if per_element:
+        gate = torch.sigmoid(projected[:, offset:offset + heads * vdim].float()).view(T, heads, vdim)
+    else:
+        gate = torch.sigmoid(projected[:, offset:offset + heads].float())[:, :, None]
+    rows = (mixed.view(T, heads, head)[..., :vdim].float() * gate * scale).reshape(T, heads * vdim).to(mixed.dtype)
+    if out is None:
+        return rows
+    out.copy_(rows)
+    return out
+
+
+def rotate_heads(projected, heads, dim, positions, inv_freq, rot_dims, scales):
+    """float32 [T, heads dim]: the first ``heads * dim`` columns of ``projected`` as heads of ``dim``, the first ``rot_dims``
+    entries of each turned by position * inv_freq (pairs i, i + rot_dims/2); ``scales`` ((count, factor), ...) multiplies
+    runs of heads by a factor each."""
+    T = projected.shape[0]
+    x = projected[:, :heads * dim].float().reshape(T, heads, dim)
+    if inv_freq is not None and rot_dims > 0:
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        half = rot_dims // 2
+        a, b = x[..., :half], x[..., half:rot_dims]
+        x = torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot_dims:]], dim=-1)
+    factor = torch.cat([torch.full((count,), float(f)) for count, f in scales]).to(x.device)
+    return (x * factor[None, :, None]).reshape(T, heads * dim).contiguous()
+
+
+def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim, max_q_len=0):
+    """S <- decay_h S + k_t v_t^T, o_t = S^T q_t per request and head, S [dim, vdim] float32 in ``state[seat]`` (zeros and
+    nothing kept for a seat below 0).  qk float32 [T, 2 heads dim] (queries, then keys); values [T, heads vdim]."""
+    T = qk.shape[0]
+    q = qk[:, :heads * dim].view(T, heads, dim)
+    k = qk[:, heads * dim:].view(T, heads, dim)
+    v = values.float().reshape(T, heads, vdim)
+    out = torch.zeros(T, heads, vdim, dtype=torch.float32, device=qk.device)
+    cu, seats = cu_q.tolist(), state_slots.tolist()
+    w = decay.float()[:, None, None]
+    for r in range(len(seats)):
+        seat = seats[r]
+        S = state[seat, :heads * dim * vdim].view(heads, dim, vdim).clone() if seat >= 0 else torch.zeros(heads, dim, vdim, device=qk.device)
+        for t in range(cu[r], cu[r + 1]):
+            S = w * S + k[t][:, :, None] * v[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        if seat >= 0:
+            state[seat, :heads * dim * vdim] = S.reshape(-1)
+    return out.view(T, heads * vdim)
 
 
 def mingru_scan(zxg, bias, state, state_slots, cu_q, width, out_dtype, max_q_len=0):
@@ -375,12 +457,18 @@ def wkv_recurrence(r, k, v, decay_logits, w0, u, state, state_slots, cu_q, heads
     return out.view(T, heads * dim)
 
 
-def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype):
+def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype, scale=1.0, into=None):
     T, inner = out.shape
     x = out.float().view(T, heads, inner // heads)
-    x = x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
+    x = (x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)).reshape(T, inner)
+    if weight is not None:
+        x = x * weight.float()
     gf = g.float()
-    return (x.reshape(T, inner) * weight.float() * (gf / (1.0 + torch.exp(-gf)))).to(out_dtype)
+    rows = (x * (gf / (1.0 + torch.exp(-gf))) * scale).to(out_dtype)
+    if into is None:
+        return rows
+    into.copy_(rows)
+    return into
 
 
 # ---- attention over a cached latent -------------------------------------------------------------------
@@ -423,13 +511,16 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
 
 
 # ---- routed feed-forward ------------------------------------------------------------------------------
-def route_top(logits, top, scale):
+def route_top(logits, top, scale, over_chosen=False):
+    if over_chosen:
+        best = torch.topk(logits.float(), top, dim=-1)
+        return best.indices.to(torch.int32), (torch.softmax(best.values, dim=-1) * scale).float()
     scores = torch.softmax(logits.float(), dim=-1)
     best = torch.topk(scores, top, dim=-1)
     return best.indices.to(torch.int32), (best.values * scale).float()
 
 
-def routed_experts(h, chosen, weights, gate_up, down, shared=None):
+def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0):
     T, D = h.shape
     f = down.shape[2]
     total = torch.zeros(T, D, dtype=torch.float32, device=h.device)
@@ -439,7 +530,11 @@ def routed_experts(h, chosen, weights, gate_up, down, shared=None):
             rows = (chosen[:, slot] == e).nonzero().flatten()
             gu = hf[rows] @ gate_up[e].float().T
             g, u = gu[:, :f], gu[:, f:]
-            act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).float()
+            if activation == "clamped":
+                g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+                act = (g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)).to(h.dtype).float()
+            else:
+                act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).float()
             total[rows] += weights[rows, slot, None] * (act @ down[e].float().T)
     if shared is not None:
         total += shared.float()
