@@ -45,6 +45,16 @@ enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_GEGLU = 5 };      // 5: th
 __device__ __forceinline__ float gate_function(float z, int act) {
     return act == 0 ? z / (1.f + expf(-z)) : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
+// The gated epilogue's value: act 0 and 1 gate_function(g) * u; act 2 the clamped form, with g <- min(g, limit) and
+// u <- clamp(u, -limit, limit): g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_value(float g, float u, int act, float limit) {
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    }
+    return gate_function(g, act) * u;
+}
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -156,7 +166,7 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out_raw, int M, int N_out, int K, int up_row_offset, int m_tiles, int n_tiles,
                     const int* __restrict__ g_tiles, const int* __restrict__ g_expert, const int* __restrict__ g_row0,
-                    const int* __restrict__ g_offsets, int w_rows, int gate_act, int* __restrict__ status) {
+                    const int* __restrict__ g_offsets, int w_rows, int gate_act, float gate_limit, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long acc_full[ACC_BUFFERS], acc_empty[ACC_BUFFERS];
@@ -263,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     float u[32];
                     tmem_load32(lane_addr + 128 + c, u);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gate_function(v[j], gate_act) * u[j];
+                    for (int j = 0; j < 32; ++j) v[j] = gated_value(v[j], u[j], gate_act, gate_limit);
                 }
                 if (row < row_end && EPI == EPI_F32) {
                     float* dst = reinterpret_cast<float*>(out_raw) + (size_t)row * N_out + n0 + c;
@@ -332,7 +342,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 template <int EPI>
 int launch(const void* x, const void* W, void* out, int M, int N, int K, int* status, cudaStream_t stream,
            const int* g_tiles = nullptr, const int* g_expert = nullptr, const int* g_row0 = nullptr, const int* g_offsets = nullptr,
-           long long w_rows_total = 0, int gate_act = 0) {
+           long long w_rows_total = 0, int gate_act = 0, float gate_limit = 0.f) {
     const int n_out = EPI == EPI_SWIGLU ? N / 2 : N;
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : 256;
     CUtensorMap map_a, map_b;
@@ -346,7 +356,7 @@ int launch(const void* x, const void* W, void* out, int M, int N, int K, int* st
     const long long total = (long long)m_tiles * n_tiles;
     const int blocks = g_tiles ? sms : (int)(total < sms ? total : sms);        // one persistent block per SM
     fe::launch(gemm_tcgen05_kernel<EPI>, blocks, THREADS, smem, stream, map_a, map_b, out, M, n_out, K, n_out,
-               m_tiles, n_tiles, g_tiles, g_expert, g_row0, g_offsets, N, gate_act, status);
+               m_tiles, n_tiles, g_tiles, g_expert, g_row0, g_offsets, N, gate_act, gate_limit, status);
     return fe_check_launch("gemm_tcgen05");
 }
 
@@ -369,10 +379,11 @@ extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, i
 
 // The grouped form: x [rows, K] sorted by expert, W [experts * N, K] (every expert's N rows; for SwiGLU its gate rows,
 // then its up rows), the row tiles of 128 from a list on the device (tiles[0] of them: tile_expert, tile_row0; offsets
-// [experts + 1] are the experts' row ranges).  epilogue 1: out float [rows, N]; 2: SwiGLU, out bfloat16 [rows, N / 2].
+// [experts + 1] are the experts' row ranges).  epilogue 1: out float [rows, N]; 2: SwiGLU, out bfloat16 [rows, N / 2]; with
+// ``limit`` > 0 the gated epilogue is the clamped one (see gated_value).
 extern "C" int fe_gemm_tcgen05_grouped(const void* x, const void* W, void* out, int rows, int experts, int N, int K, int epilogue,
                                        const int* tiles, const int* tile_expert, const int* tile_row0, const int* offsets,
-                                       int* status, cudaStream_t stream) {
+                                       float limit, int* status, cudaStream_t stream) {
     FE_REQUIRE(rows >= 1 && experts >= 1 && N >= 1 && K >= 8, "gemm_tcgen05 (grouped): bad sizes rows=%d N=%d K=%d", rows, N, K);
     FE_REQUIRE(K % 8 == 0, "gemm_tcgen05 (grouped): K = %d must be a multiple of 8 (rows must start on 16-byte boundaries)", K);
     FE_REQUIRE((((size_t)x | (size_t)W | (size_t)out) & 15) == 0, "gemm_tcgen05 (grouped): operands must be 16-byte aligned");
@@ -381,7 +392,8 @@ extern "C" int fe_gemm_tcgen05_grouped(const void* x, const void* W, void* out, 
     if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total);
     if (epilogue == EPI_SWIGLU) {
         FE_REQUIRE(N % 2 == 0, "gemm_tcgen05 (grouped): SwiGLU needs an even number of weight rows, got %d", N);
-        return launch<EPI_SWIGLU>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total);
+        return launch<EPI_SWIGLU>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total,
+                                  limit > 0.f ? 2 : 0, limit);
     }
     FE_REQUIRE(false, "gemm_tcgen05 (grouped): unknown epilogue %d", epilogue);
 }

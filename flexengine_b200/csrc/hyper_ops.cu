@@ -514,7 +514,9 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
                                                 const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot,
                                                 int qk_norm, float eps, const int* __restrict__ slot_mapping, T* __restrict__ kc,
                                                 T* __restrict__ vc, T* __restrict__ q_out, int T_tokens, int heads, int kv_heads, int dim,
-                                                int vdim, int head, int ps, long long num_slots, int n_seats, int* __restrict__ status) {
+                                                int vdim, int head, int ps, long long num_slots, int n_seats, int* __restrict__ status,
+                                                const float* __restrict__ q_weight, const float* __restrict__ k_weight, float temp_coef,
+                                                int temp_every) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float staged[];
@@ -600,6 +602,10 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
                     inv = rsqrtf(ss / (float)hd + eps);
                 }
             }
+            // after the norm: its weight (one table for the query heads, one for the key heads) and, for a query, the
+            // temperature of its position, 1 + coef ln(floor((p + 1) / every) + 1)
+            const float* wt = what == 0 ? q_weight : (what == 1 ? k_weight : nullptr);
+            if (what == 0 && temp_coef != 0.f) inv *= 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.f);
             T* dst = nullptr;
             if (what == 0) {
                 dst = q_out + (size_t)t * heads * head + (size_t)index * head;
@@ -618,11 +624,11 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
                 if (PER > 0) {
                     float v[LIMIT];
 #pragma unroll
-                    for (int e = 0; e < LIMIT; ++e) v[e] = buf[lane * LIMIT + e] * inv;
+                    for (int e = 0; e < LIMIT; ++e) v[e] = buf[lane * LIMIT + e] * inv * (wt ? wt[lane * LIMIT + e] : 1.f);
                     Lanes<T, LIMIT>::store(dst + lane * LIMIT, v);
                     for (int c = hd + lane; c < head; c += 32) dst[c] = from_float<T>(0.f);
                 } else {
-                    for (int c = lane; c < head; c += 32) dst[c] = from_float<T>(c < hd ? buf[c] * inv : 0.f);
+                    for (int c = lane; c < head; c += 32) dst[c] = from_float<T>(c < hd ? buf[c] * inv * (wt ? wt[c] : 1.f) : 0.f);
                 }
             }
             __syncwarp();
@@ -645,7 +651,7 @@ static int launch_qkv_prepare(const void* proj, long long ld, const float* conv,
                               const int* seats, const int* cu_q, const int* token_req, const int* positions, const float* inv_freq, int rot,
                               int qk_norm, float eps, const int* slot_mapping, void* kc, void* vc, void* q_out, int T_tokens, int heads,
                               int kv_heads, int dim, int vdim, int head, int ps, long long num_slots, int n_seats, int* status,
-                              cudaStream_t stream) {
+                              const float* q_weight, const float* k_weight, float temp_coef, int temp_every, cudaStream_t stream) {
     const int per_token = heads + 2 * kv_heads;
     // up to 16 warps share out the token's heads evenly: 24 heads are two rounds of 12 warps
     const int rounds = (per_token + 15) / 16;
@@ -662,7 +668,8 @@ static int launch_qkv_prepare(const void* proj, long long ld, const float* conv,
 #define FE_LAUNCH_QKV_PREPARE(PER)                                                                                                   \
     fe::launch(qkv_conv_rope_norm_cache_kernel<T, PER>, T_tokens, warps * 32, smem, stream, (const T*)proj, ld, conv, history,     \
                history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (T*)kc, (T*)vc,  \
-               (T*)q_out, T_tokens, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status)
+               (T*)q_out, T_tokens, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status, q_weight, k_weight, temp_coef,     \
+               temp_every)
     if (per == 1) FE_LAUNCH_QKV_PREPARE(1);
     else if (per == 2) FE_LAUNCH_QKV_PREPARE(2);
     else if (per == 4) FE_LAUNCH_QKV_PREPARE(4);
@@ -676,7 +683,10 @@ extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const
                                            int taps, const int* seats, const int* cu_q, const int* token_req, const int* positions,
                                            const float* inv_freq, int rot, int qk_norm, float eps, const int* slot_mapping, void* kc,
                                            void* vc, void* q_out, int T, int heads, int kv_heads, int dim, int vdim, int head, int ps,
-                                           long long num_slots, int n_seats, int dtype, int* status, cudaStream_t stream) {
+                                           long long num_slots, int n_seats, int dtype, int* status, const float* q_weight,
+                                           const float* k_weight, float temp_coef, int temp_every, cudaStream_t stream) {
+    FE_REQUIRE((q_weight == nullptr) == (k_weight == nullptr) && (temp_coef == 0.f || temp_every > 0),
+               "qkv_conv_rope_norm_cache: norm weights come in pairs, and a temperature needs a positive period");
     FE_REQUIRE(T >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && head >= dim && head >= vdim && head <= 1024,
                "qkv_conv_rope_norm_cache: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d head=%d", heads, kv_heads, dim, vdim, head);
     FE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim && ps > 0 && taps >= 0, "qkv_conv_rope_norm_cache: bad rotation, page size or taps");
@@ -688,20 +698,21 @@ extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const
     if (dtype == FE_F32)
         return launch_qkv_prepare<float>(proj, ld, conv, history, history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot,
                                          qk_norm, eps, slot_mapping, kc, vc, q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots,
-                                         n_seats, status, stream);
+                                         n_seats, status, q_weight, k_weight, temp_coef, temp_every, stream);
     if (dtype == FE_BF16)
         return launch_qkv_prepare<bf16>(proj, ld, conv, history, history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot,
                                         qk_norm, eps, slot_mapping, kc, vc, q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots,
-                                        n_seats, status, stream);
+                                        n_seats, status, q_weight, k_weight, temp_coef, temp_every, stream);
     FE_REQUIRE(false, "qkv_conv_rope_norm_cache: unknown dtype %d", dtype);
 }
 
 // ---------------------------------------------------------------------------------------------
-// out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(gates[t * ld + h]): every head's output times its gate, the padding of
-// the attention kernels' head size dropped on the way.
+// out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(gate) * scale: every head's output times its gate, the padding of the
+// attention kernels' head size dropped on the way.  The gate of entry c of head h is gates[t * ld + h] (one a head), or
+// gates[t * ld + h * vdim + c] with ``per_element``.  A row of out is ldo entries long (a view of a wider buffer).
 template <typename T>
 __global__ void head_gate_kernel(const T* __restrict__ mixed, const T* __restrict__ gates, long long ld, T* __restrict__ out,
-                                 long long total, int heads, int head, int vdim) {
+                                 long long ldo, long long total, int heads, int head, int vdim, int per_element, float scale) {
     griddep_wait();
     griddep_launch_dependents();
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
@@ -709,14 +720,15 @@ __global__ void head_gate_kernel(const T* __restrict__ mixed, const T* __restric
         const long long th = e / vdim;
         const int h = (int)(th % heads);
         const long long t = th / heads;
-        out[e] = from_float<T>(to_float(mixed[(t * heads + h) * head + c]) * sigmoidf(to_float(gates[t * ld + h])));
+        const float g = to_float(gates[t * ld + (per_element ? h * vdim + c : h)]);
+        out[t * ldo + h * vdim + c] = from_float<T>(to_float(mixed[(t * heads + h) * head + c]) * sigmoidf(g) * scale);
     }
 }
 
-// The same, eight columns of one head a thread (vdim and head multiples of 8): 16- or 32-byte loads and stores.
+// The same, eight columns of one head a thread (vdim, head and the row lengths multiples of 8): 16- or 32-byte loads and stores.
 template <typename T>
 __global__ void head_gate_vec_kernel(const T* __restrict__ mixed, const T* __restrict__ gates, long long ld, T* __restrict__ out,
-                                     long long groups, int heads, int head, int vdim) {
+                                     long long ldo, long long groups, int heads, int head, int vdim, int per_element, float scale) {
     griddep_wait();
     griddep_launch_dependents();
     const int per_head = vdim >> 3;
@@ -725,41 +737,47 @@ __global__ void head_gate_vec_kernel(const T* __restrict__ mixed, const T* __res
         const long long th = e / per_head;
         const int h = (int)(th % heads);
         const long long t = th / heads;
-        const float g = sigmoidf(to_float(gates[t * ld + h]));
-        float v[8];
+        float v[8], g[8];
         load8<T>(mixed + (t * heads + h) * head + c, v);
+        if (per_element) {
+            load8<T>(gates + t * ld + h * vdim + c, g);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= g;
-        store8<T>(out + (t * heads + h) * vdim + c, v);
+            for (int i = 0; i < 8; ++i) v[i] *= sigmoidf(g[i]) * scale;
+        } else {
+            const float one = sigmoidf(to_float(gates[t * ld + h])) * scale;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= one;
+        }
+        store8<T>(out + t * ldo + h * vdim + c, v);
     }
 }
 
-extern "C" int fe_head_gate(const void* mixed, const void* gates, long long ld, void* out, int T, int heads, int head, int vdim,
-                            int dtype, cudaStream_t stream) {
-    FE_REQUIRE(T >= 0 && heads > 0 && head >= vdim && vdim > 0, "head_gate: bad sizes");
+extern "C" int fe_head_gate(const void* mixed, const void* gates, long long ld, void* out, long long ldo, int T, int heads, int head,
+                            int vdim, int per_element, float scale, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && heads > 0 && head >= vdim && vdim > 0 && ldo >= (long long)heads * vdim, "head_gate: bad sizes");
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "head_gate: unknown dtype %d", dtype);
     const long long total = (long long)T * heads * vdim;
     if (total == 0) return 0;
-    if (vdim % 8 == 0 && head % 8 == 0 && (((size_t)mixed | (size_t)out) & 31) == 0 && (dtype == FE_F32 || dtype == FE_BF16)) {
+    const bool gates_fit = !per_element || (ld % 8 == 0 && ((size_t)gates & 31) == 0);
+    if (vdim % 8 == 0 && head % 8 == 0 && ldo % 8 == 0 && gates_fit && (((size_t)mixed | (size_t)out) & 31) == 0) {
         const long long groups = total / 8, want = (groups + 255) / 256;
         const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
         if (dtype == FE_F32)
-            fe::launch(head_gate_vec_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, groups,
-                       heads, head, vdim);
+            fe::launch(head_gate_vec_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, ldo,
+                       groups, heads, head, vdim, per_element, scale);
         else
-            fe::launch(head_gate_vec_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, groups,
-                       heads, head, vdim);
+            fe::launch(head_gate_vec_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, ldo,
+                       groups, heads, head, vdim, per_element, scale);
         return fe_check_launch("head_gate");
     }
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
     if (dtype == FE_F32)
-        fe::launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, total, heads,
-                   head, vdim);
-    else if (dtype == FE_BF16)
-        fe::launch(head_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, total, heads,
-                   head, vdim);
+        fe::launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, ldo, total,
+                   heads, head, vdim, per_element, scale);
     else
-        FE_REQUIRE(false, "head_gate: unknown dtype %d", dtype);
+        fe::launch(head_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, ldo, total,
+                   heads, head, vdim, per_element, scale);
     return fe_check_launch("head_gate");
 }
 

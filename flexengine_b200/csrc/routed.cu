@@ -18,9 +18,21 @@ using namespace fe;
 
 constexpr int ROUTE_MAX_EXPERTS = 1024;
 
-// One warp per token.  ties go to the lower expert index.
+// What an expert does with its gate and up products.  limit 0: silu(g) * u.  limit > 0 (the clamped form):
+// g <- min(g, limit), u <- clamp(u, -limit, limit), then g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float expert_activation(float g, float u, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;
+}
+
+// One warp per token.  ties go to the lower expert index.  ``over_chosen`` 0: the weights are the chosen experts' shares of
+// the softmax over all logits; 1: the ``top`` largest logits are chosen and the weights are the softmax over those alone.
 __global__ void route_top_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weights,
-                                 int T, int experts, int top, float scale) {
+                                 int T, int experts, int top, float scale, int over_chosen) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float rows[];               // [warps][experts]
@@ -35,13 +47,14 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
     float sum = 0.f;
     for (int e = lane; e < experts; e += 32) {
         const float p = expf(z[e] - m);
-        s[e] = p;
+        s[e] = over_chosen ? z[e] : p;            // what the experts are ranked by
         sum += p;
     }
     sum = warp_sum(sum);
     __syncwarp();
+    float chosen_sum = 0.f;
     for (int c = 0; c < top; ++c) {
-        float best = -1.f;
+        float best = -CUDART_INF_F;
         int at = experts;
         for (int e = lane; e < experts; e += 32)
             if (s[e] > best) { best = s[e]; at = e; }
@@ -51,23 +64,30 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
+        if (at >= experts) at = 0;                // nothing left to rank (logits that are not numbers): a weight of zero
         if (lane == 0) {
+            const float share = over_chosen ? expf(best - m) : best;      // m is the largest logit, the first one chosen
             chosen[(size_t)t * top + c] = at;
-            weights[(size_t)t * top + c] = best / sum * scale;
-            s[at] = -2.f;
+            weights[(size_t)t * top + c] = over_chosen ? share : share / sum * scale;
+            chosen_sum += share;
+            s[at] = -CUDART_INF_F;
         }
         __syncwarp();
+    }
+    if (over_chosen && lane == 0) {
+        const float inv = scale / chosen_sum;
+        for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] *= inv;
     }
 }
 
 extern "C" int fe_route_top(const float* logits, int* chosen, float* weights, int T, int experts, int top, float scale,
-                            cudaStream_t stream) {
+                            int over_chosen, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && top >= 1 && top <= experts,
                "route_top: bad sizes (experts %d, top %d; at most %d experts)", experts, top, ROUTE_MAX_EXPERTS);
     if (T == 0) return 0;
     const int warps = 4;
     fe::launch(route_top_kernel, (T + warps - 1) / warps, warps * 32, (size_t)warps * experts * sizeof(float), stream, logits,
-               chosen, weights, T, experts, top, scale);
+               chosen, weights, T, experts, top, scale, over_chosen);
     return fe_check_launch("route_top");
 }
 
@@ -124,7 +144,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
                       void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
-                      const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+                      const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     griddep_wait();
     griddep_launch_dependents();
     if ((int)blockIdx.y >= tiles[0]) return;
@@ -192,7 +212,7 @@ routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_r
             const size_t at = (size_t)(row0 + r) * N + gn;
             if (GATED) {
                 const float g = acc[i][j];
-                reinterpret_cast<T*>(out)[at] = from_float<T>(g / (1.f + expf(-g)) * acu[i][j]);
+                reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, acu[i][j], limit));
             } else {
                 reinterpret_cast<float*>(out)[at] = acc[i][j];
             }
@@ -211,7 +231,7 @@ template <typename T, bool GATED, int ROWS>
 __global__ void __launch_bounds__(FEW_WARPS * 32)
 routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
-                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     griddep_wait();
     griddep_launch_dependents();
     if ((int)blockIdx.y >= tiles[0]) return;
@@ -292,7 +312,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
                 const float u = GATED ? warp_sum(acu[c][r]) : 0.f;
                 if (lane == 0 && nbase + c < N) {
                     const size_t at = (size_t)(row0 + r) * N + nbase + c;
-                    if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(g / (1.f + expf(-g)) * u);
+                    if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, u, limit));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -325,7 +345,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
             const float u = GATED ? warp_sum(acu[r]) : 0.f;
             if (lane == 0 && r < rows) {
                 const size_t at = (size_t)(row0 + r) * N + n;
-                if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(g / (1.f + expf(-g)) * u);
+                if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, u, limit));
                 else reinterpret_cast<float*>(out)[at] = g;
             }
         }
@@ -340,7 +360,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(128)
 routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
-                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     using namespace nvcuda;
     griddep_wait();
     griddep_launch_dependents();
@@ -431,7 +451,7 @@ routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pa
                 if (r < rows && gn < N) {
                     const size_t at = (size_t)(row0 + r) * N + gn;
                     const float g = stage[warp][0][rr][cc];
-                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(g / (1.f + expf(-g)) * stage[warp][GATED ? 1 : 0][rr][cc]);
+                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(expert_activation(g, stage[warp][GATED ? 1 : 0][rr][cc], limit));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -457,7 +477,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(256)
 routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
                            void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
-                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     using namespace nvcuda;
     griddep_wait();
     griddep_launch_dependents();
@@ -553,7 +573,7 @@ routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ p
                 if (r < rows && gn < N) {
                     const size_t at = (size_t)(row0 + r) * N + gn;
                     const float g = mine[rr * 20 + cc];
-                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(g / (1.f + expf(-g)) * mine[16 * 20 + rr * 20 + cc]);
+                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(expert_activation(g, mine[16 * 20 + rr * 20 + cc], limit));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -590,9 +610,11 @@ extern "C" long long fe_routed_experts_workspace(int T, int top, int experts, in
 }
 
 // h [T, D]; chosen, weights [T, top]; gate_up [experts, 2F, D]; down [experts, D, F]; shared [T, D] or null; out [T, D].
+// limit: 0 for silu(gate) * up, else the clamped activation (see expert_activation).
 extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* weights, const void* gate_up, const void* down,
                                  const void* shared, void* out, void* workspace, long long workspace_bytes, int T, int top,
-                                 int experts, int D, int F, int dtype, int* status, cudaStream_t stream) {
+                                 int experts, int D, int F, int dtype, float limit, int* status, cudaStream_t stream) {
+    FE_REQUIRE(limit >= 0.f, "routed_experts: the activation's limit is 0 (plain silu) or positive");
     FE_REQUIRE(T >= 0 && top >= 1 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && D > 0 && F > 0, "routed_experts: bad sizes");
     FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "routed_experts: unknown dtype %d", dtype);
     if (T == 0) return 0;
@@ -625,9 +647,9 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     const int *c_offsets = offsets, *c_tiles = tiles, *c_expert = tile_expert, *c_row0 = tile_row0;
 #define FE_ROUTED_PRODUCTS(KERNEL1, KERNEL2, TYPE, GRID1, GRID2, THREADS, SMEM1, SMEM2)                                                   \
     fe::launch(KERNEL1, GRID1, THREADS, SMEM1, stream, (const TYPE*)h, c_pairs, top, (const TYPE*)gate_up, (void*)act, c_offsets, c_tiles, \
-               c_expert, c_row0, F, D);                                                                                                   \
+               c_expert, c_row0, F, D, limit);                                                                                            \
     fe::launch(KERNEL2, GRID2, THREADS, SMEM2, stream, (const TYPE*)act, c_none, top, (const TYPE*)down, (void*)y, c_offsets, c_tiles,    \
-               c_expert, c_row0, D, F)
+               c_expert, c_row0, D, F, 0.f)
     if (few) {
         const int few_tiles = (int)((pairs + few_rows - 1) / few_rows + experts);
         const int per_block = FEW_WARPS * FEW_COLS;

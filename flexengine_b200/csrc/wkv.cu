@@ -303,37 +303,43 @@ extern "C" int fe_wkv_recurrence(const void* r, const void* k, const void* v, co
 }
 
 // ---------------------------------------------------------------------------------------------
-// y[t, head] = o[t, head] / sqrt(mean(o[t, head]^2) + eps) * weight * silu(g): one warp per (token, head).
+// y[t, head] = o[t, head] / sqrt(mean(o[t, head]^2) + eps) * weight * silu(g) * scale: one warp per (token, head).
+// ``weight`` may be null (a unit norm).  A row of g is ldg entries long and a row of out ldo (views of wider buffers).
 template <typename T>
 __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight, const T* __restrict__ g,
-                                         T* __restrict__ out, float eps, long long pairs, int heads, int d) {
+                                         long long ldg, T* __restrict__ out, long long ldo, float eps, float scale, long long pairs,
+                                         int heads, int d) {
     griddep_wait();
     griddep_launch_dependents();
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (warp >= pairs) return;
     const int lane = threadIdx.x & 31;
     const int head = (int)(warp % heads);
+    const long long t = warp / heads;
     const float* x = o + warp * d;
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) ss += x[i] * x[i];
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)d + eps);
+    const float inv = rsqrtf(ss / (float)d + eps) * scale;
     for (int i = lane; i < d; i += 32) {
-        const float gate = to_float(g[warp * d + i]);
-        out[warp * d + i] = from_float<T>(x[i] * inv * weight[head * d + i] * (gate / (1.f + expf(-gate))));
+        const float gate = to_float(g[t * ldg + head * d + i]);
+        const float w = weight ? weight[head * d + i] : 1.f;
+        out[t * ldo + head * d + i] = from_float<T>(x[i] * inv * w * (gate / (1.f + expf(-gate))));
     }
 }
 
-extern "C" int fe_head_rmsnorm_gate(const float* o, const float* weight, const void* g, void* out, float eps, int T, int heads,
-                                    int d, int dtype, cudaStream_t stream) {
-    FE_REQUIRE(T >= 0 && heads > 0 && d > 0, "head_rmsnorm_gate: bad sizes");
+extern "C" int fe_head_rmsnorm_gate(const float* o, const float* weight, const void* g, long long ldg, void* out, long long ldo, float eps,
+                                    float scale, int T, int heads, int d, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && heads > 0 && d > 0 && ldg >= (long long)heads * d && ldo >= (long long)heads * d, "head_rmsnorm_gate: bad sizes");
     if (T == 0) return 0;
     const long long pairs = (long long)T * heads;
     const unsigned blocks = (unsigned)((pairs + 3) / 4);
     if (dtype == FE_F32)
-        fe::launch(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, o, weight, (const float*)g, (float*)out, eps, pairs, heads, d);
+        fe::launch(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, o, weight, (const float*)g, ldg, (float*)out, ldo, eps, scale,
+                   pairs, heads, d);
     else if (dtype == FE_BF16)
-        fe::launch(head_rmsnorm_gate_kernel<bf16>, blocks, 128, 0, stream, o, weight, (const bf16*)g, (bf16*)out, eps, pairs, heads, d);
+        fe::launch(head_rmsnorm_gate_kernel<bf16>, blocks, 128, 0, stream, o, weight, (const bf16*)g, ldg, (bf16*)out, ldo, eps, scale,
+                   pairs, heads, d);
     else
         FE_REQUIRE(false, "head_rmsnorm_gate: unknown dtype %d", dtype);
     return fe_check_launch("head_rmsnorm_gate");

@@ -141,11 +141,59 @@ def _upcoming(tensor, rows: int, limit: int = UPCOMING_BYTES):
     return _ptr(tensor), _c_ll(min(tensor.numel() * tensor.element_size(), limit))
 
 
-def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None):
+def _post_norm(residual, delta, post, weight, eps, out, rows, n_out, extra=None):
+    """One launch of the kernel for branches that end in a norm of their own (csrc/post_norm.cu); see its callers."""
+    T, H = residual.shape
+    post_w, post_eps, bias = post if post is not None else (None, 0.0, None)
+    _need_cuda(residual, delta, weight, rows, post_w, bias, extra)
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream is contiguous float32")
+    for vector in (weight, post_w, bias):
+        if vector is not None and (vector.dtype != torch.float32 or vector.numel() != H):
+            raise TypeError("norm weights and biases are float32 vectors of the stream's width")
+    if delta is not None and (delta.dtype not in (torch.float32, out.dtype) or tuple(delta.shape) != (T, H) or not delta.is_contiguous()):
+        raise ValueError("a branch output is contiguous, shaped like the residual, float32 or in the compute dtype")
+    extra_cols = 0
+    if extra is not None:
+        if extra.dtype != torch.float32 or extra.dim() != 2 or extra.shape[0] != T or not extra.is_contiguous():
+            raise ValueError("extra rows are contiguous float32 [T, columns]")
+        extra_cols = extra.shape[1]
+    _run(_core(), "fe_post_norm", _ptr(residual), _ptr(delta), _c_int(_code(delta.dtype) if delta is not None else 0), _ptr(bias),
+         _ptr(post_w), _c_float(post_eps), _ptr(weight), _c_float(eps), _ptr(out), _c_ll(out.stride(0)), _ptr(rows), _c_int(n_out),
+         _c_int(H), _ptr(extra), _c_int(extra_cols), _c_int(T), _c_int(_code(out.dtype)), _stream())
+    return out
+
+
+def residual_concat(residual, delta, extra, out_dtype, post=None):
+    """residual += delta (through a norm of its own with ``post`` = (weight, eps, bias still to add)), then the rows
+    [residual | extra] in ``out_dtype``: what a product reads that re-enters the stream from the stream and other float32
+    rows of the same tokens."""
+    T, H = residual.shape
+    out = torch.empty((T, H + extra.shape[1]), dtype=out_dtype, device=residual.device)
+    return _post_norm(residual, delta, post, None, 0.0, out, None, T, extra=extra)
+
+
+def scale_softcap(logits, scale, cap):
+    """logits <- cap * tanh(logits * scale / cap) in place (cap 0: logits * scale); float32."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise TypeError("scale_softcap: logits are contiguous float32")
+    _run(_core(), "fe_scale_softcap", _ptr(logits), _c_ll(logits.numel()), _c_float(scale), _c_float(cap), _stream())
+    return logits
+
+
+def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None, post=None):
     """Fused residual add + RMSNorm.  rows=None: residual += delta in place (all rows) and every row
     is normalised; rows given: only those rows are read (residual[rows] + delta[rows]), nothing is
     written back.  ``upcoming``: the weight matrix that the next kernel streams; in a decode step extra
-    blocks of this kernel, which barely touches memory, ask for its start to be brought into L2."""
+    blocks of this kernel, which barely touches memory, ask for its start to be brought into L2.
+    ``post`` = (weight, eps, bias or None): the branch output goes through a norm of its own on its way into the stream,
+    w_b (delta + bias) / rms(delta + bias); delta may then be float32 whatever the compute dtype."""
+    if post is not None and delta is not None:
+        T, H = residual.shape
+        n_out = T if rows is None else rows.numel()
+        out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+        return _post_norm(residual, delta, post, weight, eps, out, rows, n_out)
     _need_cuda(residual, delta, weight, rows)
     T, H = residual.shape
     if residual.dtype != torch.float32 or weight.dtype != torch.float32:
@@ -337,14 +385,24 @@ def linear_swiglu(x, w, intermediate, upcoming=None):
 GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
-def gated_activation(gate_up, intermediate, activation):
-    """act(gate) * up of rows [gate | up]; act "silu" or "gelu_tanh" (the tanh form of GELU), float arithmetic."""
-    _need_cuda(gate_up)
+def gated_activation(gate_up, intermediate, activation, bias=None, out_dtype=None):
+    """act(gate) * up of rows [gate | up]; act "silu" or "gelu_tanh" (the tanh form of GELU), float arithmetic.  ``bias``
+    (float32 [2 * intermediate]) is added to both first; the rows may then be a float32 product and ``out_dtype`` the
+    compute dtype."""
+    _need_cuda(gate_up, bias)
     T = gate_up.shape[0]
     if gate_up.shape[1] != 2 * intermediate or not gate_up.is_contiguous():
         raise ValueError("gated_activation: input must be contiguous [T, 2 * intermediate]")
     if activation not in GATE_ACTIVATIONS:
         raise ValueError(f"unknown gate activation {activation!r}; known: {sorted(GATE_ACTIVATIONS)}")
+    if bias is not None or (out_dtype is not None and out_dtype != gate_up.dtype):
+        out_dtype = out_dtype or gate_up.dtype
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != 2 * intermediate):
+            raise ValueError("gated_activation: the bias is float32 [2 * intermediate]")
+        out = torch.empty((T, intermediate), dtype=out_dtype, device=gate_up.device)
+        _run(_core(), "fe_gated_activation_bias", _ptr(gate_up), _c_int(_code(gate_up.dtype)), _ptr(bias), _ptr(out), _c_int(T),
+             _c_int(intermediate), _c_int(GATE_ACTIVATIONS[activation]), _c_int(_code(out_dtype)), _stream())
+        return out
     out = torch.empty((T, intermediate), dtype=gate_up.dtype, device=gate_up.device)
     _run(_core(), "fe_gated_activation", _ptr(gate_up), _ptr(out), _c_int(T), _c_int(intermediate),
          _c_int(GATE_ACTIVATIONS[activation]), _c_int(_code(gate_up.dtype)), _stream())
@@ -731,7 +789,8 @@ def token_shift(h, mu, kept, state_slots, cu_q, token_request):
 
 
 def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, token_request, positions, inv_freq, rot_dims,
-                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size,
+                             q_weight=None, k_weight=None, temp=None):
     """What attention does between its projection and its scores, in one kernel (csrc/hyper_ops.cu).  ``projected``
     [T, >= channels] holds q | k | v (``heads`` and ``kv_heads`` heads of ``dim``, ``kv_heads`` of ``vdim``).  A causal
     convolution of ``taps`` taps over time per channel (``conv`` [taps, channels] float32, tap by tap, None for none; ``history``
@@ -739,8 +798,15 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
     first ``rot_dims`` entries of every query and key head turned by position * inv_freq (pairs i, i + rot_dims/2), queries
     and keys divided by their root mean square (``qk_norm``), keys and values into their cache slots
     [pages, kv_heads, page_size, head] (slot_mapping None: no write) and the queries returned [T, heads head], all padded
-    with zeros from dim or vdim to ``head``."""
-    _need_cuda(projected, conv, history, state_slots, cu_q, token_request, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    with zeros from dim or vdim to ``head``.  ``q_weight``, ``k_weight`` (float32 [dim]): weights of the query and the key
+    norm, shared by the heads.  ``temp`` = (coef, every): the query at position p is then multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1)."""
+    _need_cuda(projected, conv, history, state_slots, cu_q, token_request, positions, inv_freq, slot_mapping, k_cache, v_cache,
+               q_weight, k_weight)
+    if (q_weight is None) != (k_weight is None) or any(w is not None and (w.dtype != torch.float32 or w.numel() != dim)
+                                                       for w in (q_weight, k_weight)):
+        raise ValueError("qkv_conv_rope_norm_cache: the norm weights are two float32 vectors of the head's query/key size")
+    temp_coef, temp_every = (float(temp[0]), int(temp[1])) if temp is not None else (0.0, 1)
     T = projected.shape[0]
     channels = (heads + kv_heads) * dim + kv_heads * vdim
     if projected.dim() != 2 or projected.shape[1] < channels or projected.stride(1) != 1:
@@ -764,21 +830,28 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
          _ptr(positions), _ptr(inv_freq), _c_int(rot_dims if inv_freq is not None else 0), _c_int(1 if qk_norm else 0), _c_float(eps),
          _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _ptr(queries), _c_int(T), _c_int(heads), _c_int(kv_heads), _c_int(dim),
          _c_int(vdim), _c_int(head), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _c_int(seats),
-         _c_int(_code(projected.dtype)), _ptr(status_word(projected.device)), _stream())
+         _c_int(_code(projected.dtype)), _ptr(status_word(projected.device)), _ptr(q_weight), _ptr(k_weight), _c_float(temp_coef),
+         _c_int(temp_every), _stream())
     return queries
 
 
-def head_gate(mixed, projected, offset, heads, head, vdim):
-    """[T, heads vdim]: out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h]); ``mixed`` [T, heads head]."""
-    _need_cuda(mixed, projected)
+def head_gate(mixed, projected, offset, heads, head, vdim, per_element=False, scale=1.0, out=None):
+    """[T, heads vdim]: out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h]) * scale; ``mixed``
+    [T, heads head].  With ``per_element`` the gate of entry j of head h is projected[t, offset + h vdim + j].  ``out``: where
+    the rows go (a view with any row stride, for rows that are written side by side with another mixer's)."""
+    _need_cuda(mixed, projected, out)
     T = mixed.shape[0]
+    gates_needed = heads * vdim if per_element else heads
     if tuple(mixed.shape) != (T, heads * head) or not mixed.is_contiguous() or projected.dtype != mixed.dtype \
-            or projected.stride(1) != 1 or projected.shape[1] < offset + heads:
+            or projected.stride(1) != 1 or projected.shape[1] < offset + gates_needed:
         raise ValueError("head_gate: shapes or dtypes do not fit")
-    out = torch.empty((T, heads * vdim), dtype=mixed.dtype, device=mixed.device)
+    if out is None:
+        out = torch.empty((T, heads * vdim), dtype=mixed.dtype, device=mixed.device)
+    elif tuple(out.shape) != (T, heads * vdim) or out.dtype != mixed.dtype or out.stride(1) != 1:
+        raise ValueError("head_gate: out is [T, heads vdim] in the compute dtype with unit column stride")
     gates = projected[:, offset:]
-    _run(_core(), "fe_head_gate", _ptr(mixed), _ptr(gates), _c_ll(projected.stride(0)), _ptr(out), _c_int(T), _c_int(heads),
-         _c_int(head), _c_int(vdim), _c_int(_code(mixed.dtype)), _stream())
+    _run(_core(), "fe_head_gate", _ptr(mixed), _ptr(gates), _c_ll(projected.stride(0)), _ptr(out), _c_ll(out.stride(0)), _c_int(T),
+         _c_int(heads), _c_int(head), _c_int(vdim), _c_int(1 if per_element else 0), _c_float(scale), _c_int(_code(mixed.dtype)), _stream())
     return out
 
 
@@ -911,17 +984,59 @@ def wkv_recurrence(r, k, v, decay_logits, w0, u, state, state_slots, cu_q, heads
     return out
 
 
-def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype):
-    """Every head of ``out`` (float32 [T, heads dim]) divided by its root mean square, times ``weight``, times silu(g)."""
-    _need_cuda(out, weight, g)
+def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype, scale=1.0, into=None):
+    """Every head of ``out`` (float32 [T, heads dim]) divided by its root mean square, times ``weight`` (None: a unit norm),
+    times silu(g), times ``scale``.  ``g`` and ``into`` (where the rows go) may be views with any row stride."""
+    _need_cuda(out, weight, g, into)
     T, inner = out.shape
-    if out.dtype != torch.float32 or weight.dtype != torch.float32 or g.dtype != out_dtype or g.shape != out.shape \
-            or not (out.is_contiguous() and g.is_contiguous()) or inner % heads:
+    if out.dtype != torch.float32 or (weight is not None and weight.dtype != torch.float32) or g.dtype != out_dtype \
+            or tuple(g.shape) != (T, inner) or not out.is_contiguous() or g.stride(1) != 1 or inner % heads:
         raise ValueError("head_rmsnorm_gate: float32 rows and weight, a gate of the same shape in the compute dtype")
-    y = torch.empty((T, inner), dtype=out_dtype, device=out.device)
-    _run(_core(), "fe_head_rmsnorm_gate", _ptr(out), _ptr(weight), _ptr(g), _ptr(y), _c_float(eps), _c_int(T), _c_int(heads),
-         _c_int(inner // heads), _c_int(_code(out_dtype)), _stream())
+    y = into if into is not None else torch.empty((T, inner), dtype=out_dtype, device=out.device)
+    if tuple(y.shape) != (T, inner) or y.dtype != out_dtype or y.stride(1) != 1:
+        raise ValueError("head_rmsnorm_gate: the rows go to [T, heads dim] in the compute dtype with unit column stride")
+    _run(_core(), "fe_head_rmsnorm_gate", _ptr(out), _ptr(weight), _ptr(g), _c_ll(g.stride(0)), _ptr(y), _c_ll(y.stride(0)),
+         _c_float(eps), _c_float(scale), _c_int(T), _c_int(heads), _c_int(inner // heads), _c_int(_code(out_dtype)), _stream())
     return y
+
+
+# ---- retention -----------------------------------------------------------------------------------------------------
+def rotate_heads(projected, heads, dim, positions, inv_freq, rot_dims, scales):
+    """float32 [T, heads dim]: the first ``heads * dim`` columns of ``projected`` (any row stride) as heads of ``dim``, the
+    first ``rot_dims`` entries of each turned by position * inv_freq (pairs i, i + rot_dims/2); ``scales``
+    ((count, factor), (count, factor)) multiplies the first run of heads by one factor and the rest by another."""
+    _need_cuda(projected, positions, inv_freq)
+    T = projected.shape[0]
+    if projected.dim() != 2 or projected.shape[1] < heads * dim or projected.stride(1) != 1:
+        raise ValueError("rotate_heads: projected is [T, >= heads dim] with unit column stride")
+    scales = tuple(scales)
+    if not 1 <= len(scales) <= 2 or sum(count for count, _ in scales) != heads:
+        raise ValueError("rotate_heads: one or two runs of heads that together are all of them")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise ValueError("inv_freq must be float32 [rot_dims / 2]")
+    out = torch.empty((T, heads * dim), dtype=torch.float32, device=projected.device)
+    _run(_core(), "fe_rotate_heads", _ptr(projected), _c_ll(projected.stride(0)), _ptr(positions), _ptr(inv_freq),
+         _c_int(rot_dims if inv_freq is not None else 0), _ptr(out), _c_int(T), _c_int(heads), _c_int(dim), _c_int(scales[0][0]),
+         _c_float(scales[0][1]), _c_float(scales[-1][1]), _c_int(_code(projected.dtype)), _stream())
+    return out
+
+
+def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim, max_q_len=0):
+    """S <- decay_h S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens (csrc/retention.cu); S [dim, vdim]
+    float32 lives in ``state[seat, : heads dim vdim]`` (zeros and nothing kept for a seat below 0).  qk float32
+    [T, 2 heads dim] (queries, then keys); values [T, heads vdim] with any row stride; returns float32 [T, heads vdim]."""
+    _need_cuda(qk, values, decay, state, state_slots, cu_q)
+    T = qk.shape[0]
+    if qk.dtype != torch.float32 or tuple(qk.shape) != (T, 2 * heads * dim) or not qk.is_contiguous() or decay.dtype != torch.float32 \
+            or decay.numel() != heads or state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[-1] < heads * dim * vdim \
+            or tuple(values.shape) != (T, heads * vdim) or values.stride(1) != 1:
+        raise ValueError("retention_scan: qk is contiguous float32 [T, 2 heads dim], values [T, heads vdim], decay float32 [heads], "
+                         "the state float32 [seats, >= heads dim vdim]")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qk.device)
+    _run(_core(), "fe_retention_scan", _ptr(qk), _ptr(values), _c_ll(values.stride(0)), _ptr(decay), _ptr(state), _c_ll(state.stride(0)),
+         _ptr(state_slots), _ptr(cu_q), _ptr(out), _c_int(cu_q.numel() - 1), _c_int(heads), _c_int(dim), _c_int(vdim),
+         _c_int(state.shape[0]), _c_int(_code(values.dtype)), _stream())
+    return out
 
 
 # ---- attention over a cached latent ------------------------------------------------------------------------------
@@ -974,9 +1089,10 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
 
 
 # ---- a routed feed-forward ---------------------------------------------------------------------------------------
-def route_top(logits, top, scale):
+def route_top(logits, top, scale, over_chosen=False):
     """(int32 [T, top], float32 [T, top]): per token the ``top`` largest softmax scores over all experts (float32, ties
-    to the lower index) times ``scale``, and their experts."""
+    to the lower index) times ``scale``, and their experts.  ``over_chosen``: the ``top`` largest logits are chosen and the
+    weights are the softmax over those alone (times ``scale``)."""
     _need_cuda(logits)
     T, experts = logits.shape
     if logits.dtype != torch.float32 or not logits.is_contiguous():
@@ -984,7 +1100,7 @@ def route_top(logits, top, scale):
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     _run(_core(), "fe_route_top", _ptr(logits), _ptr(chosen), _ptr(weights), _c_int(T), _c_int(experts), _c_int(top),
-         _c_float(scale), _stream())
+         _c_float(scale), _c_int(1 if over_chosen else 0), _stream())
     return chosen, weights
 
 
@@ -999,7 +1115,7 @@ def routed_tcgen05_ok(h, pairs, H, F) -> bool:
             and min(H, F) >= ROUTED_TCGEN05_MIN_K and h.data_ptr() % 16 == 0)
 
 
-def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared):
+def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit=0.0):
     """The routed feed-forward with its products on tcgen05 tensor cores: plan (counting sort, row tiles of 128 per
     expert), the rows of h gathered into sorted order, gate/up with the activation in the epilogue, down into float32,
     combination.  Everything stays on the device."""
@@ -1021,20 +1137,22 @@ def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared):
     _run(core, "fe_routed_gather", _ptr(h), _ptr(pair_of_row), _c_int(top), _ptr(rows), _c_int(pairs), _c_ll(H * 2), _stream())
     act = torch.empty((pairs, F), dtype=torch.bfloat16, device=dev)
     _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(rows), _ptr(gate_up), _ptr(act), _c_int(pairs), _c_int(experts), _c_int(2 * F),
-         _c_int(H), _c_int(EPI_SWIGLU), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _ptr(status), _stream())
+         _c_int(H), _c_int(EPI_SWIGLU), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _c_float(limit), _ptr(status), _stream())
     y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
     _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(act), _ptr(down), _ptr(y), _c_int(pairs), _c_int(experts), _c_int(H), _c_int(F),
-         _c_int(EPI_F32), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _ptr(status), _stream())
+         _c_int(EPI_F32), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _c_float(0.0), _ptr(status), _stream())
     out = torch.empty((T, H), dtype=h.dtype, device=dev)
     _run(core, "fe_routed_combine", _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(shared), _ptr(out), _c_int(T), _c_int(top),
          _c_int(H), _c_int(_code(h.dtype)), _stream())
     return out
 
 
-def routed_experts(h, chosen, weights, gate_up, down, shared=None):
+def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0):
     """out[t] = sum_c weights[t, c] * down_e( silu(gate_e h_t) * up_e h_t ) with e = chosen[t, c], plus ``shared`` [T, H] if
-    given; gate_up [experts, 2F, H] ([gate; up] per expert), down [experts, H, F].  The (token, choice) pairs are sorted
-    by expert on the device and every expert multiplies its own rows (csrc/routed.cu): nothing comes back to the host."""
+    given; gate_up [experts, 2F, H] ([gate; up] per expert), down [experts, H, F].  ``activation`` "clamped": with
+    g = min(gate_e h_t, limit) and u = clamp(up_e h_t, -limit, limit) an expert is down_e( g sigmoid(1.702 g) (u + 1) ).
+    The (token, choice) pairs are sorted by expert on the device and every expert multiplies its own rows (csrc/routed.cu):
+    nothing comes back to the host."""
     _need_cuda(h, chosen, weights, gate_up, down, shared)
     T, H = h.shape
     experts, F2, _ = gate_up.shape
@@ -1044,15 +1162,18 @@ def routed_experts(h, chosen, weights, gate_up, down, shared=None):
             or chosen.dtype != torch.int32 or weights.dtype != torch.float32 \
             or (shared is not None and (shared.dtype != h.dtype or shared.shape != h.shape or not shared.is_contiguous())):
         raise ValueError("routed_experts: shapes or dtypes do not fit")
+    if activation not in ("silu", "clamped") or (activation == "clamped" and not limit > 0.0):
+        raise ValueError("routed_experts: the activation is 'silu' or 'clamped' with a positive limit")
+    limit = float(limit) if activation == "clamped" else 0.0
     if routed_tcgen05_ok(h, T * top, H, F):
-        return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared)
+        return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit)
     lib = _core()
     need = lib.fe_routed_experts_workspace(_c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)))
     work = torch.empty(need, dtype=torch.uint8, device=h.device)
     out = torch.empty((T, H), dtype=h.dtype, device=h.device)
     _run(lib, "fe_routed_experts", _ptr(h), _ptr(chosen), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(shared), _ptr(out),
          _ptr(work), _c_ll(need), _c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)),
-         _ptr(status_word(h.device)), _stream())
+         _c_float(limit), _ptr(status_word(h.device)), _stream())
     return out
 
 

@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # compiles only that
 GROUPS = {
     "core": ["errors.cu", "elementwise.cu", "attention_simt.cu", "gemm_fp32.cu", "sampling.cu", "stream_ops.cu", "wkv.cu",
-             "latent.cu", "routed.cu", "hyper_ops.cu"],
+             "latent.cu", "routed.cu", "hyper_ops.cu", "post_norm.cu", "retention.cu"],
     # elementwise.cu once more: the layer executor launches its kernels from inside this library
     "bf16": ["errors.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "elementwise.cu",
              "layer_executor.cu"],
