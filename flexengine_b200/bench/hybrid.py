@@ -1,5 +1,6 @@
-"""``--workload fuvozen|fuvuvik``: prefill and decode throughput of one of these designs at a few sizes that resemble a real
-model's layers (random weights), beside a Qwen2 decoder of equal width, depth and vocabulary, and, at one size, an
+"""``--workload fuvozen|fuvuvik|fedutar``: prefill and decode throughput of one of these designs at a few sizes that resemble a
+real model's layers (random weights), beside the closest existing model at equal width, depth and vocabulary (a Qwen2
+decoder; for Fedutar the Fuvozen design, which also has a recurrence with a matrix state and routed experts), and, at one size, an
 operation-by-operation table of both: time, the bytes and flops of the work, and how far each operation is from the
 roofline of the measured peaks (time / max(bytes / copy rate, flops / bf16 rate)).
 
@@ -55,7 +56,29 @@ def fuvuvik_config(width, layers, vocab, heads):
             "layers": stack}
 
 
-DESIGNS = {"fuvozen": ("Fuvozen", fuvozen_config), "fuvuvik": ("Fuvuvik", fuvuvik_config)}
+def fedutar_config(width, layers, vocab, heads):
+    """``layers`` runs of a layer: the first two layers run twice in a row (a junction before each pass), the others once.
+    Every layer has softmax attention (heads of 128 in groups of four, a query temperature that steps every 512 positions)
+    beside retention (width / 128 heads of 64 x 128, half of a head rotated); feed-forwards in turns: dense of 2.5 x width
+    with biases, then 8 experts of 1.25 x width of which a token uses 2.  A layer run multiplies a token by about
+    15 width^2 weights, as a Fuvozen layer does on average."""
+    distinct = max(2, layers - 2)
+    r_heads = max(1, width // 128)
+    stack = []
+    for i in range(distinct):
+        mixer = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                          "q_temp": {"coef": 0.1, "every": 512}},
+                 "right": {"heads": r_heads, "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** -(5 + h % 6) for h in range(r_heads)],
+                           "rot": {"base": 10000.0, "dims": 32}},
+                 "left_scale": 1.0, "right_scale": 1.0}
+        mlp = {"kind": "dense", "ff": width * 5 // 2} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": width * 5 // 4, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+        stack.append({"type": "parallel", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Fedutar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 2, "times": 2}, "layers": stack}
+
+
+DESIGNS = {"fuvozen": ("Fuvozen", fuvozen_config), "fuvuvik": ("Fuvuvik", fuvuvik_config), "fedutar": ("Fedutar", fedutar_config)}
 
 
 def qwen2_config(width, layers, vocab, heads):
@@ -66,6 +89,9 @@ def qwen2_config(width, layers, vocab, heads):
                 intermediate_size=width * 8 // 3 // 256 * 256, vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6,
                 max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False, hidden_act="silu", eos_token_id=None)
 
+
+# the model a design is measured beside (default: the Qwen2 decoder)
+BESIDE = {"fedutar": ("fuvozen", "Fuvozen", fuvozen_config)}
 
 SIZES = {"1k": (1024, 8, 32000, 8), "2k": (2048, 8, 32000, 16), "4k": (4096, 4, 32000, 32)}
 
@@ -128,6 +154,12 @@ class TimedOps:
             elif name == "wkv_recurrence":
                 flops = 6.0 * args[0].shape[0] * args[9] * args[10] * args[10]
                 nbytes = args[0].numel() * (3 * args[0].element_size() + 8) + 2 * 4 * (args[8].numel() - 1) * args[9] * args[10] * args[10]
+            elif name == "retention_scan":
+                # per token and head: the state's update and its product with the query; the state of a request read and written once
+                heads, d, dv = args[6], args[7], args[8]
+                tokens, requests = args[0].shape[0], args[5].numel() - 1
+                flops = 4.0 * tokens * heads * d * dv
+                nbytes = tokens * (2 * heads * d * 4 + heads * dv * (args[1].element_size() + 4)) + 2 * 4 * requests * heads * d * dv
             elif name == "stream_rmsnorm":
                 # the streams are read, and written back when a sublayer's output goes in; its output and gate are read
                 update = kwargs.get("update")
@@ -188,6 +220,7 @@ def run(args) -> int:
     sizes = [args.size] if getattr(args, "size", None) else list(SIZES)
     design, design_config = DESIGNS[args.workload]
     key = args.workload
+    other, other_name, other_config = BESIDE.get(key, ("qwen2", "Qwen2", qwen2_config))
 
     def measure(cfg, vocab, provider=None, steps=args.steps, warmup=max(args.warmup, 3)):
         _typed, plan, model = random_model(cfg, seed=0, dtype="bfloat16", device=dev)
@@ -236,20 +269,20 @@ def run(args) -> int:
     for name in sizes:
         width, layers, vocab, heads = SIZES[name]
         results[name] = {key: measure(design_config(width, layers, vocab, heads), vocab),
-                         "qwen2": measure(qwen2_config(width, layers, vocab, heads), vocab)}
-        launches += results[name][key].pop("launches") + results[name]["qwen2"].pop("launches")
+                         other: measure(other_config(width, layers, vocab, heads), vocab)}
+        launches += results[name][key].pop("launches") + results[name][other].pop("launches")
     if args.kernels:
         width, layers, vocab, heads = SIZES[sizes[-1] if getattr(args, "size", None) else "2k"]
         # as many layers as show every kind of layer the design has
         tables[key] = measure(design_config(width, 2 if key == "fuvozen" else 4, vocab, heads), vocab, TimedOps(ops, torch))
-        tables["qwen2"] = measure(qwen2_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
+        tables[other] = measure(other_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
     sampler.stop()
     first = results[sizes[0]][key]
     line = {"metric": f"decode tokens/s ({design} design, size {sizes[0]}, batch {BATCH}, {PROMPT}-token prompts)",
             "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: random token ids, random weights", "impl": "ours",
-            "config": {"model": f"{design} beside Qwen2 at equal width, depth and vocabulary", "sizes": {k: list(v) for k, v in SIZES.items() if k in sizes},
+            "config": {"model": f"{design} beside {other_name} at equal width, depth and vocabulary", "sizes": {k: list(v) for k, v in SIZES.items() if k in sizes},
                        "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_page": PAGE, "parallelism": "single GPU",
                        "peaks": peak_source},
             "sizes": results, "gpu_launches": launches, "clocks": sampler.summary(timer.windows)}
