@@ -4,11 +4,12 @@
 //   rotate_heads      float rows of heads from a projection: the first ``rot`` entries of a head turned by
 //                     position * inv_freq (pairs i, i + rot/2), runs of heads times a factor each
 //   retention_scan    the recurrence token by token over the step's portions, the state in registers
-//   retention_chunks  the same for long portions in blocks of tokens: inside a block of C tokens
-//                       o_a = a^(a+1) S_0^T q_a + sum_(b <= a) a^(a-b) (q_a . k_b) v_b
+//   retention_chunks  the same for long portions in blocks of C = 64 tokens.  Inside a block that starts from S_0
+//                       o_n = a^(n+1) S_0^T q_n + sum_(b <= n) a^(n-b) (q_n . k_b) v_b
 //                       S_C = a^C S_0 + sum_b a^(C-1-b) k_b v_b^T
-//                     so that the blocks of a portion are summed independently and then chained
-//   retention_decode  a step of one token a request: rotation, recurrence, the head's unit norm and the gate in one kernel
+//                     so three launches do a step: every block's own sum of k v^T (independent of the others), the chain
+//                     S_0 -> S_C -> ... over a portion's blocks (elementwise), and every block's outputs from the state
+//                     before it (independent again).  The products are tiled 64 x 64 over shared memory, 4 x 4 a thread.
 #define FE_PDL_CLASS 128
 #include "common.cuh"
 
@@ -161,6 +162,220 @@ int dispatch_scan(const float* qk, const void* values, long long ldv, const floa
 #undef FE_SCAN
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Long portions in blocks of CHUNK tokens.  Block c of request r has row cu_q[r] / CHUNK + r + c of ``sums``
+// ([rows, heads d dv] float): the rows of different requests never meet, and T / CHUNK + requests rows hold a step.
+constexpr int CHUNK = 64;                // tokens a block
+constexpr int TILE = 64;                 // key channels or value channels a tile
+constexpr int PITCH = CHUNK + 4;         // a transposed tile's row: float4 reads stay aligned, stores spread over banks
+static_assert(CHUNK == TILE, "a block of tokens and a tile of channels are loaded by the same loops");
+
+__device__ __forceinline__ size_t chunk_row(const int* __restrict__ cu_q, int r) { return (size_t)(cu_q[r] / CHUNK + r); }
+
+// sums[row][head] <- sum_b a^(len-1-b) k_b v_b^T over the block's len tokens.  Grid (block of tokens, request,
+// head x tile of key channels x tile of value channels), 256 threads as 16 x 16, a thread 4 key x 4 value channels.
+template <typename TV>
+__global__ void __launch_bounds__(256)
+retention_chunk_sums_kernel(const float* __restrict__ qk, const TV* __restrict__ values, long long ldv, const float* __restrict__ decay,
+                            const int* __restrict__ cu_q, float* __restrict__ sums, int heads, int d, int dv, int nd, int nv) {
+    griddep_wait();
+    griddep_launch_dependents();
+    __shared__ __align__(16) float ks[CHUNK * TILE];
+    __shared__ __align__(16) float vs[CHUNK * TILE];
+    __shared__ float pw[CHUNK];
+    const int c = blockIdx.x, r = blockIdx.y;
+    int z = blockIdx.z;
+    const int vt = z % nv;
+    z /= nv;
+    const int dt = z % nd, head = z / nd;
+    const int begin = cu_q[r] + c * CHUNK, end = cu_q[r + 1];
+    if (begin >= end) return;
+    const int len = min(CHUNK, end - begin);
+    const int tid = threadIdx.x;
+    if (tid < CHUNK) pw[tid] = tid < len ? (float)pow((double)decay[head], (double)(len - 1 - tid)) : 0.f;
+    __syncthreads();
+    const size_t row = 2 * (size_t)heads * d;
+    for (int e = tid; e < CHUNK * TILE; e += 256) {
+        const int b = e / TILE, i = e - b * TILE;
+        const int gi = dt * TILE + i, gj = vt * TILE + i;
+        const bool in = b < len;
+        ks[e] = (in && gi < d) ? pw[b] * qk[(size_t)(begin + b) * row + (size_t)heads * d + (size_t)head * d + gi] : 0.f;
+        vs[e] = (in && gj < dv) ? to_float(values[(size_t)(begin + b) * ldv + (size_t)head * dv + gj]) : 0.f;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[4][4] = {};
+    for (int b = 0; b < len; ++b) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + b * TILE + ty * 4);
+        const float4 v4 = *reinterpret_cast<const float4*>(vs + b * TILE + tx * 4);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(kk[x], vv[y], acc[x][y]);
+    }
+    float* to = sums + ((chunk_row(cu_q, r) + c) * heads + head) * (size_t)d * dv;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int gi = dt * TILE + ty * 4 + x;
+        if (gi >= d) continue;
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+            const int gj = vt * TILE + tx * 4 + y;
+            if (gj < dv) to[(size_t)gi * dv + gj] = acc[x][y];
+        }
+    }
+}
+
+// One thread an entry of the state: S walks the portion's blocks, leaving in each block's row what S was BEFORE that
+// block in place of the block's sum, and ends in the seat.
+__global__ void __launch_bounds__(256)
+retention_chunk_chain_kernel(const float* __restrict__ decay, float* state, long long state_stride, const int* __restrict__ seats,
+                             const int* __restrict__ cu_q, float* sums, int heads, int d, int dv, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int r = blockIdx.x;
+    const size_t per = (size_t)heads * d * dv;
+    const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+    const int n = cu_q[r + 1] - cu_q[r];
+    if (e >= per || n <= 0) return;
+    const int head = (int)(e / ((size_t)d * dv));
+    const int blocks = (n + CHUNK - 1) / CHUNK;
+    const double a = (double)decay[head];
+    const float whole = (float)pow(a, (double)CHUNK), last = (float)pow(a, (double)(n - (blocks - 1) * CHUNK));
+    const int seat = seats[r];
+    float* mine = (seat >= 0 && seat < n_seats) ? state + (size_t)seat * state_stride + e : nullptr;
+    float S = mine ? *mine : 0.f;
+    float* p = sums + chunk_row(cu_q, r) * per + e;
+    for (int c = 0; c < blocks; ++c, p += per) {
+        const float u = *p;
+        *p = S;
+        S = fmaf(c == blocks - 1 ? last : whole, S, u);
+    }
+    if (mine) *mine = S;
+}
+
+// A block's outputs for a tile of value channels: W = (Q K^T) with entry (n, b) times a^(n-b) where b <= n, else 0;
+// out = diag(a^(n+1)) Q S_0 + W V.  Q, K and S_0 pass through shared memory in tiles of key channels; W takes the keys' place.
+// Grid (block of tokens, request, head x tile of value channels), 256 threads as 16 x 16, a thread 4 tokens x 4 columns.
+constexpr size_t CHUNK_OUT_SMEM = ((size_t)2 * TILE * PITCH + (size_t)TILE * TILE + (size_t)CHUNK * TILE + CHUNK + 4) * sizeof(float);
+
+template <typename TV>
+__global__ void __launch_bounds__(256)
+retention_chunk_out_kernel(const float* __restrict__ qk, const TV* __restrict__ values, long long ldv, const float* __restrict__ decay,
+                           const int* __restrict__ cu_q, const float* __restrict__ sums, float* __restrict__ out, int heads, int d, int dv,
+                           int nd, int nv) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ __align__(16) float smem[];
+    float* qT = smem;                            // [TILE][PITCH]: key channel i of token n at i * PITCH + n
+    float* kT = qT + TILE * PITCH;               // the same of the keys; later W as [b][n]
+    float* sS = kT + TILE * PITCH;               // [TILE][TILE] the state before the block, key channel x value channel
+    float* vS = sS + TILE * TILE;                // [CHUNK][TILE]
+    float* pw = vS + CHUNK * TILE;               // [CHUNK + 1] powers of the decay
+    const int c = blockIdx.x, r = blockIdx.y;
+    const int vt = blockIdx.z % nv, head = blockIdx.z / nv;
+    const int begin = cu_q[r] + c * CHUNK, end = cu_q[r + 1];
+    if (begin >= end) return;
+    const int len = min(CHUNK, end - begin);
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    if (tid <= CHUNK) pw[tid] = (float)pow((double)decay[head], (double)tid);
+    for (int e = tid; e < CHUNK * TILE; e += 256) {
+        const int b = e / TILE, j = e - b * TILE, gj = vt * TILE + j;
+        vS[e] = (b < len && gj < dv) ? to_float(values[(size_t)(begin + b) * ldv + (size_t)head * dv + gj]) : 0.f;
+    }
+    const size_t row = 2 * (size_t)heads * d;
+    const float* before = sums + ((chunk_row(cu_q, r) + c) * heads + head) * (size_t)d * dv;
+    float W[4][4] = {}, O[4][4] = {};
+    for (int dt = 0; dt < nd; ++dt) {
+        __syncthreads();
+        for (int e = tid; e < CHUNK * TILE; e += 256) {
+            const int n = e / TILE, i = e - n * TILE, gi = dt * TILE + i;
+            const bool in = n < len && gi < d;
+            const float* src = qk + (size_t)(begin + n) * row + (size_t)head * d + gi;
+            qT[i * PITCH + n] = in ? src[0] : 0.f;
+            kT[i * PITCH + n] = in ? src[(size_t)heads * d] : 0.f;
+            const int gj = vt * TILE + i;                                       // here n walks key channels, i value channels
+            sS[e] = (dt * TILE + n < d && gj < dv) ? before[(size_t)(dt * TILE + n) * dv + gj] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int i = 0; i < TILE; ++i) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qT + i * PITCH + ty * 4);
+            const float4 k4 = *reinterpret_cast<const float4*>(kT + i * PITCH + tx * 4);
+            const float4 s4 = *reinterpret_cast<const float4*>(sS + i * TILE + tx * 4);
+            const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    W[x][y] = fmaf(qq[x], kk[y], W[x][y]);
+                    O[x][y] = fmaf(qq[x], ss[y], O[x][y]);
+                }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int y = 0; y < 4; ++y) {
+        const int b = tx * 4 + y;
+        float w[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int n = ty * 4 + x;
+            w[x] = b <= n ? W[x][y] * pw[n - b] : 0.f;
+        }
+        *reinterpret_cast<float4*>(kT + b * PITCH + ty * 4) = make_float4(w[0], w[1], w[2], w[3]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) O[x][y] *= pw[ty * 4 + x + 1];
+    __syncthreads();
+    const int seen = min(len, ty * 4 + 4);                                       // tokens after a thread's last one weigh nothing
+    for (int b = 0; b < seen; ++b) {
+        const float4 w4 = *reinterpret_cast<const float4*>(kT + b * PITCH + ty * 4);
+        const float4 v4 = *reinterpret_cast<const float4*>(vS + b * TILE + tx * 4);
+        const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) O[x][y] = fmaf(ww[x], vv[y], O[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int n = ty * 4 + x;
+        if (n >= len) continue;
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+            const int gj = vt * TILE + tx * 4 + y;
+            if (gj < dv) out[(size_t)(begin + n) * heads * dv + (size_t)head * dv + gj] = O[x][y];
+        }
+    }
+}
+
+template <typename TV>
+int launch_chunks(const float* qk, const void* values, long long ldv, const float* decay, float* state, long long state_stride,
+                  const int* seats, const int* cu_q, float* out, float* sums, int requests, int most_blocks, int heads, int d, int dv,
+                  int n_seats, cudaStream_t stream) {
+    static bool opted = false;
+    if (!opted) {
+        const cudaError_t err = cudaFuncSetAttribute(retention_chunk_out_kernel<TV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)CHUNK_OUT_SMEM);
+        FE_REQUIRE(err == cudaSuccess, "retention_chunks: %s", cudaGetErrorString(err));
+        opted = true;
+    }
+    const int nd = (d + TILE - 1) / TILE, nv = (dv + TILE - 1) / TILE;
+    const size_t per = (size_t)heads * d * dv;
+    fe::launch(retention_chunk_sums_kernel<TV>, dim3(most_blocks, requests, heads * nd * nv), 256, 0, stream, qk, (const TV*)values, ldv,
+               decay, cu_q, sums, heads, d, dv, nd, nv);
+    fe::launch(retention_chunk_chain_kernel, dim3(requests, (unsigned)((per + 255) / 256)), 256, 0, stream, decay, state, state_stride,
+               seats, cu_q, sums, heads, d, dv, n_seats);
+    fe::launch(retention_chunk_out_kernel<TV>, dim3(most_blocks, requests, heads * nv), 256, CHUNK_OUT_SMEM, stream, qk, (const TV*)values,
+               ldv, decay, cu_q, (const float*)sums, out, heads, d, dv, nd, nv);
+    return fe_check_launch("retention_chunks");
+}
+
 }  // namespace
 
 // out float [T, heads dim]; proj [T, >= heads dim] with rows ld entries long; the first ``first_heads`` heads are multiplied by
@@ -197,4 +412,26 @@ extern "C" int fe_retention_scan(const float* qk, const void* values, long long 
     if (dtype == FE_F32)
         return dispatch_scan<float>(qk, values, ldv, decay, state, state_stride, seats, cu_q, out, requests, heads, d, dv, n_seats, stream);
     return dispatch_scan<bf16>(qk, values, ldv, decay, state, state_stride, seats, cu_q, out, requests, heads, d, dv, n_seats, stream);
+}
+
+// The same as fe_retention_scan for steps with long portions, in blocks of 64 tokens (three launches).  ``sums`` is scratch:
+// float [tokens / 64 + requests, heads d dv] (fe_retention_chunk_rows says how many rows); ``most_tokens`` is the longest
+// portion of the step or more.
+extern "C" int fe_retention_chunk_tokens() { return CHUNK; }
+
+extern "C" int fe_retention_chunks(const float* qk, const void* values, long long ldv, const float* decay, float* state,
+                                   long long state_stride, const int* seats, const int* cu_q, float* out, float* sums, int requests,
+                                   int most_tokens, int heads, int d, int dv, int n_seats, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(requests >= 0 && requests <= 65535 && heads > 0 && d > 0 && dv > 0 && n_seats >= 0 && most_tokens >= 0 &&
+                   (long long)heads * d * dv <= state_stride && ldv >= (long long)heads * dv &&
+                   (long long)heads * ((d + TILE - 1) / TILE) * ((dv + TILE - 1) / TILE) <= 65535,
+               "retention_chunks: bad sizes (heads %d, key size %d, value size %d, %d requests)", heads, d, dv, requests);
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "retention_chunks: unknown dtype %d", dtype);
+    if (requests == 0 || most_tokens == 0) return 0;
+    const int most_blocks = (most_tokens + CHUNK - 1) / CHUNK;
+    if (dtype == FE_F32)
+        return launch_chunks<float>(qk, values, ldv, decay, state, state_stride, seats, cu_q, out, sums, requests, most_blocks, heads, d, dv,
+                                    n_seats, stream);
+    return launch_chunks<bf16>(qk, values, ldv, decay, state, state_stride, seats, cu_q, out, sums, requests, most_blocks, heads, d, dv,
+                               n_seats, stream);
 }

@@ -1021,6 +1021,10 @@ def rotate_heads(projected, heads, dim, positions, inv_freq, rot_dims, scales):
     return out
 
 
+# a step whose longest portion has this many tokens or more runs the recurrence in blocks of tokens
+RETENTION_CHUNKS_FROM = 32
+
+
 def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim, max_q_len=0):
     """S <- decay_h S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens (csrc/retention.cu); S [dim, vdim]
     float32 lives in ``state[seat, : heads dim vdim]`` (zeros and nothing kept for a seat below 0).  qk float32
@@ -1033,6 +1037,14 @@ def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim
         raise ValueError("retention_scan: qk is contiguous float32 [T, 2 heads dim], values [T, heads vdim], decay float32 [heads], "
                          "the state float32 [seats, >= heads dim vdim]")
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qk.device)
+    if max_q_len >= RETENTION_CHUNKS_FROM:
+        # long portions: blocks of tokens summed side by side and chained (three launches) instead of a walk token by token
+        block = _core().fe_retention_chunk_tokens()
+        sums = torch.empty((T // block + cu_q.numel() - 1, heads * dim * vdim), dtype=torch.float32, device=qk.device)
+        _run(_core(), "fe_retention_chunks", _ptr(qk), _ptr(values), _c_ll(values.stride(0)), _ptr(decay), _ptr(state),
+             _c_ll(state.stride(0)), _ptr(state_slots), _ptr(cu_q), _ptr(out), _ptr(sums), _c_int(cu_q.numel() - 1), _c_int(max_q_len),
+             _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(state.shape[0]), _c_int(_code(values.dtype)), _stream())
+        return out
     _run(_core(), "fe_retention_scan", _ptr(qk), _ptr(values), _c_ll(values.stride(0)), _ptr(decay), _ptr(state), _c_ll(state.stride(0)),
          _ptr(state_slots), _ptr(cu_q), _ptr(out), _c_int(cu_q.numel() - 1), _c_int(heads), _c_int(dim), _c_int(vdim),
          _c_int(state.shape[0]), _c_int(_code(values.dtype)), _stream())

@@ -524,6 +524,42 @@ def test_retention_over_a_portion_of_thousands_of_tokens(device, dtype):
     close(got, want, dtype, "a long portion", bars=(1e-4, 0.1))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("value_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,dim,vdim,decay", [(2, 64, 128, [0.97, 1.0]), (3, 24, 40, [0.5, 0.999, 0.9]), (1, 130, 72, [0.99]),
+                                                   (2, 72, 200, [0.0, 0.98])])
+def test_recurrence_in_blocks_of_tokens_against_the_walk(value_dtype, heads, dim, vdim, decay):
+    """The kernels that sum blocks of tokens side by side and chain them, against the recurrence written out token by token:
+    portions of one token, one token less and more than a block, several blocks and a ragged last one in ONE step; a seat that
+    already holds a state, a fresh one, a request without a seat; key and value sizes that are no multiples of a tile; a decay
+    of exactly one and of exactly zero."""
+    import flexengine_b200.ops as ops
+    device = "cuda:0"
+    lengths = [1, 63, 64, 65, 333, 130]
+    seats = [2, 0, -1, 5, 1, 4]
+    T, per = sum(lengths), heads * dim * vdim
+    g = torch.Generator().manual_seed(7)
+    qk = torch.randn(T, 2 * heads * dim, generator=g) * dim ** -0.25
+    projected = (torch.randn(T, heads * vdim + 9, generator=g)).to(getattr(torch, value_dtype))
+    values = projected[:, 4:4 + heads * vdim]                                  # a view with a row stride of its own
+    state = torch.randn(6, per + 3, generator=g)
+    w = torch.tensor(decay, dtype=torch.float32)
+    cu = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32)
+    slots = torch.tensor(seats, dtype=torch.int32)
+    want_state = state.clone()
+    want = kernel_refs.retention_scan(qk, values, w, want_state, slots, cu, heads, dim, vdim)
+    dev = [t.to(device) for t in (qk, projected, w, state, slots, cu)]
+    got_state = dev[3]
+    got = ops.retention_scan(dev[0], dev[1][:, 4:4 + heads * vdim], dev[2], got_state, dev[4], dev[5], heads, dim, vdim, max_q_len=max(lengths))
+    scale = want.abs().max()
+    assert (got.cpu() - want).abs().max() <= 2e-5 * scale
+    assert (got_state.cpu() - want_state).abs().max() <= 2e-5 * want_state.abs().max()
+    # and the walk itself, which a step of short portions takes
+    walked_state = state.to(device)
+    walked = ops.retention_scan(dev[0], dev[1][:, 4:4 + heads * vdim], dev[2], walked_state, dev[4], dev[5], heads, dim, vdim, max_q_len=1)
+    assert (walked.cpu() - want).abs().max() <= 2e-5 * scale and (walked_state.cpu() - want_state).abs().max() <= 2e-5 * want_state.abs().max()
+
+
 @pytest.mark.parametrize("device,dtype", CASES)
 @pytest.mark.parametrize("shape", [((4, 2, 16, 24, (0.3, 5)), (3, 16, 8, [0.9, 0.95, 0.99], 8), 1.2, 0.9),
                                    ((1, 1, 48, 40, None), (1, 40, 24, [0.98], 20), 1.0, 0.5),
