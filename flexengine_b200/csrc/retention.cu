@@ -69,6 +69,7 @@ retention_scan_kernel(const float* __restrict__ qk, const TV* __restrict__ value
     const int req = blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int columns = (blockDim.x >> 5) * 4;
+    float* dots = vs + SCAN_TILE * columns;       // [TILE] q_t . k_t
     const int j0 = blockIdx.z * columns;
     const int group = lane >> 2;
     const int local = warp * 4 + (lane & 3);
@@ -101,6 +102,18 @@ retention_scan_kernel(const float* __restrict__ qk, const TV* __restrict__ value
             if (j0 + c < dv) vs[e] = to_float(values[(size_t)(t0 + tt) * ldv + (size_t)head * dv + j0 + c]);
         }
         __syncthreads();
+        // o_t = a S_(t-1)^T q_t + (q_t . k_t) v_t: the token's own share as ONE factor for all value channels, as the blocks of
+        // tokens have it, so that a head whose q . k nearly cancels keeps its direction through the unit norm that follows
+        for (int tt = warp; tt < count; tt += blockDim.x >> 5) {
+            float dot = 0.f;
+            for (int i = lane; i < d; i += 32) {
+                const int at = tt * ROW + (i / IPT) * GP + i % IPT;
+                dot = fmaf(qs[at], ks[at], dot);
+            }
+            dot = warp_sum(dot);
+            if (lane == 0) dots[tt] = dot;
+        }
+        __syncthreads();
         for (int tt = 0; tt < count; ++tt) {
             const float vj = vs[tt * columns + local];
             const float* qt = qs + tt * ROW + group * GP;
@@ -113,14 +126,14 @@ retention_scan_kernel(const float* __restrict__ qk, const TV* __restrict__ value
                 const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
                 for (int y = 0; y < 4; ++y) {
-                    S[x + y] = fmaf(a, S[x + y], kk[y] * vj);
                     acc = fmaf(qq[y], S[x + y], acc);
+                    S[x + y] = fmaf(a, S[x + y], kk[y] * vj);
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (group == 0 && own) out[(size_t)(t0 + tt) * heads * dv + (size_t)head * dv + j] = acc;
+            if (group == 0 && own) out[(size_t)(t0 + tt) * heads * dv + (size_t)head * dv + j] = fmaf(a, acc, dots[tt] * vj);
         }
         __syncthreads();
     }
@@ -145,7 +158,7 @@ int launch_scan(const float* qk, const void* values, long long ldv, const float*
     int warps = (head_warps + slices - 1) / slices;
     if (warps > 16) warps = 16;
     slices = (head_warps + warps - 1) / warps;
-    const size_t smem = ((size_t)2 * SCAN_TILE * 8 * (IPT + 4) + (size_t)SCAN_TILE * warps * 4) * sizeof(float);
+    const size_t smem = ((size_t)2 * SCAN_TILE * 8 * (IPT + 4) + (size_t)SCAN_TILE * warps * 4 + SCAN_TILE) * sizeof(float);
     fe::launch(retention_scan_kernel<TV, IPT>, dim3(requests, heads, slices), warps * 32, smem, stream, qk, (const TV*)values, ldv, decay,
                state, state_stride, seats, cu_q, out, heads, d, dv, n_seats);
     return fe_check_launch("retention_scan");
@@ -248,10 +261,17 @@ retention_chunk_chain_kernel(const float* __restrict__ decay, float* state, long
     float* mine = (seat >= 0 && seat < n_seats) ? state + (size_t)seat * state_stride + e : nullptr;
     float S = mine ? *mine : 0.f;
     float* p = sums + chunk_row(cu_q, r) * per + e;
-    for (int c = 0; c < blocks; ++c, p += per) {
-        const float u = *p;
-        *p = S;
-        S = fmaf(c == blocks - 1 ? last : whole, S, u);
+    constexpr int AHEAD = 8;                      // the sums of so many blocks are asked for at once: the chain waits on memory
+    for (int c0 = 0; c0 < blocks; c0 += AHEAD, p += AHEAD * per) {
+        float u[AHEAD];
+#pragma unroll
+        for (int x = 0; x < AHEAD; ++x) u[x] = c0 + x < blocks ? __ldcs(p + x * per) : 0.f;
+#pragma unroll
+        for (int x = 0; x < AHEAD; ++x) {
+            if (c0 + x >= blocks) break;
+            p[x * per] = S;
+            S = fmaf(c0 + x == blocks - 1 ? last : whole, S, u[x]);
+        }
     }
     if (mine) *mine = S;
 }
