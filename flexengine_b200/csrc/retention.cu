@@ -10,6 +10,7 @@
 //                     so three launches do a step: every block's own sum of k v^T (independent of the others), the chain
 //                     S_0 -> S_C -> ... over a portion's blocks (elementwise), and every block's outputs from the state
 //                     before it (independent again).  The products are tiled 64 x 64 over shared memory, 4 x 4 a thread.
+//   retention_decode  a step of one token a request: rotation, recurrence, the head's unit norm and the gate in one kernel
 #define FE_PDL_CLASS 128
 #include "common.cuh"
 
@@ -396,6 +397,95 @@ int launch_chunks(const float* qk, const void* values, long long ldv, const floa
     return fe_check_launch("retention_chunks");
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// A step of ONE token a request: rotation, recurrence, the head's unit norm and the gate in one kernel.  Block per
+// (request, head); its threads are ``groups`` runs of key channels x ``columns`` value channels, so that the state's rows
+// are read and written side by side and many of them are in flight; the runs' shares of S^T q meet in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+retention_decode_kernel(const T* __restrict__ proj, long long ld, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                        int rot, float key_scale, const float* __restrict__ decay, float* state, long long state_stride,
+                        const int* __restrict__ seats, T* __restrict__ out, long long ldo, float eps, float scale, int heads, int d,
+                        int dv, int n_seats, int groups) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ __align__(16) float smem[];
+    const int columns = blockDim.x / groups;
+    float* qs = smem;                               // [d] rotated query
+    float* ks = qs + d;                             // [d] rotated key, scaled
+    float* os = ks + d;                             // [dv] the head's output before its norm
+    float* part = os + dv;                          // [groups][columns]
+    float* red = part + groups * columns;           // [33]
+    const int r = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const T* row = proj + (size_t)r * ld;
+    const T* qrow = row + (size_t)head * d;
+    const T* krow = row + (size_t)heads * d + (size_t)head * d;
+    const int half = rot >> 1;
+    for (int i = tid; i < d; i += blockDim.x) {
+        float q = to_float(qrow[i]), k = to_float(krow[i]);
+        if (i < rot) {
+            const bool low = i < half;
+            const int other = low ? i + half : i - half;
+            float sn, cs;
+            sincosf((float)positions[r] * inv_freq[low ? i : i - half], &sn, &cs);
+            const float qo = to_float(qrow[other]), ko = to_float(krow[other]);
+            q = low ? q * cs - qo * sn : q * cs + qo * sn;
+            k = low ? k * cs - ko * sn : k * cs + ko * sn;
+        }
+        qs[i] = q;
+        ks[i] = k * key_scale;
+    }
+    __syncthreads();
+    float dot = 0.f;
+    for (int i = 0; i < d; ++i) dot = fmaf(qs[i], ks[i], dot);
+    const int seat = seats[r];
+    float* mine = (seat >= 0 && seat < n_seats) ? state + (size_t)seat * state_stride + (size_t)head * d * dv : nullptr;
+    const float a = decay[head];
+    const int g = tid / columns, jj = tid - g * columns;
+    const int per = (d + groups - 1) / groups;
+    const int i0 = g * per, i1 = min(d, i0 + per);
+    const T* vrow = row + 2 * (size_t)heads * d + (size_t)head * dv;
+    float ss = 0.f;
+    for (int j0 = 0; j0 < dv; j0 += columns) {
+        const int j = j0 + jj;
+        const bool own = g < groups && j < dv;
+        const float vj = own ? to_float(vrow[j]) : 0.f;
+        float acc = 0.f;
+        if (own && mine) {
+            float* col = mine + j;
+            for (int i = i0; i < i1; i += 8) {          // eight rows asked for before any is written
+                float sv[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) sv[x] = i + x < i1 ? col[(size_t)(i + x) * dv] : 0.f;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    if (i + x >= i1) break;
+                    acc = fmaf(qs[i + x], sv[x], acc);
+                    col[(size_t)(i + x) * dv] = fmaf(a, sv[x], ks[i + x] * vj);
+                }
+            }
+        }
+        if (g < groups) part[g * columns + jj] = acc;
+        __syncthreads();
+        if (g == 0 && j < dv) {
+            float sum = 0.f;
+            for (int x = 0; x < groups; ++x) sum += part[x * columns + jj];
+            const float o = fmaf(a, sum, dot * vj);
+            os[j] = o;
+            ss = fmaf(o, o, ss);
+        }
+        __syncthreads();
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)dv + eps) * scale;
+    const T* grow = vrow + (size_t)heads * dv;
+    for (int j = tid; j < dv; j += blockDim.x) {
+        const float gate = to_float(grow[j]);
+        out[(size_t)r * ldo + (size_t)head * dv + j] = from_float<T>(os[j] * inv * (gate / (1.f + expf(-gate))));
+    }
+}
+
 }  // namespace
 
 // out float [T, heads dim]; proj [T, >= heads dim] with rows ld entries long; the first ``first_heads`` heads are multiplied by
@@ -454,4 +544,31 @@ extern "C" int fe_retention_chunks(const float* qk, const void* values, long lon
                                     n_seats, stream);
     return launch_chunks<bf16>(qk, values, ldv, decay, state, state_stride, seats, cu_q, out, sums, requests, most_blocks, heads, d, dv,
                                n_seats, stream);
+}
+
+// A step of one token a request in one kernel.  proj [R, >= 2 heads d + 2 heads dv] = q | k | v | g in ``dtype`` with rows ld
+// entries long; the keys are multiplied by key_scale after the rotation; out [R, >= heads dv] in ``dtype`` with rows ldo long gets
+// every head divided by its root mean square, times silu(g), times scale.
+extern "C" int fe_retention_decode(const void* proj, long long ld, const int* positions, const float* inv_freq, int rot, float key_scale,
+                                   const float* decay, float* state, long long state_stride, const int* seats, void* out, long long ldo,
+                                   float eps, float scale, int requests, int heads, int d, int dv, int n_seats, int dtype,
+                                   cudaStream_t stream) {
+    FE_REQUIRE(requests >= 0 && heads > 0 && heads <= 65535 && d > 0 && dv > 0 && n_seats >= 0 && rot >= 0 && rot % 2 == 0 && rot <= d &&
+                   (long long)heads * d * dv <= state_stride && ld >= 2LL * heads * d + 2LL * heads * dv && ldo >= (long long)heads * dv,
+               "retention_decode: bad sizes (heads %d, key size %d, value size %d, %d turned)", heads, d, dv, rot);
+    FE_REQUIRE(rot == 0 || inv_freq != nullptr, "retention_decode: a rotation needs its frequencies");
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "retention_decode: unknown dtype %d", dtype);
+    if (requests == 0) return 0;
+    int columns = ((dv < 256 ? dv : 256) + 31) / 32 * 32;
+    int groups = 512 / columns;
+    groups = groups < 1 ? 1 : (groups > d ? d : groups);
+    const size_t smem = ((size_t)2 * d + dv + (size_t)groups * columns + 33) * sizeof(float);
+    FE_REQUIRE(smem <= 48 * 1024, "retention_decode: key size %d and value size %d need more shared memory than a block has", d, dv);
+    if (dtype == FE_F32)
+        fe::launch(retention_decode_kernel<float>, dim3(requests, heads), groups * columns, smem, stream, (const float*)proj, ld, positions,
+                   inv_freq, rot, key_scale, decay, state, state_stride, seats, (float*)out, ldo, eps, scale, heads, d, dv, n_seats, groups);
+    else
+        fe::launch(retention_decode_kernel<bf16>, dim3(requests, heads), groups * columns, smem, stream, (const bf16*)proj, ld, positions,
+                   inv_freq, rot, key_scale, decay, state, state_stride, seats, (bf16*)out, ldo, eps, scale, heads, d, dv, n_seats, groups);
+    return fe_check_launch("retention_decode");
 }

@@ -1051,6 +1051,32 @@ def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim
     return out
 
 
+def retention_decode(projected, heads, dim, vdim, positions, inv_freq, rot_dims, key_scale, decay, state, state_slots, eps, out_dtype,
+                     scale=1.0, into=None):
+    """A step of ONE token a request in one kernel (csrc/retention.cu): ``projected`` [R, >= 2 heads dim + 2 heads vdim] =
+    q | k | v | g (any row stride); rotation of q and k, the keys times ``key_scale``, S <- decay_h S + k v^T in
+    ``state[seat]`` (zeros and nothing kept for a seat below 0), o = S^T q, every head of o divided by its root mean square,
+    times silu(g), times ``scale``.  Returns [R, heads vdim] in ``out_dtype`` (``into`` where given, a view with any row stride)."""
+    _need_cuda(projected, positions, inv_freq, decay, state, state_slots, into)
+    R = projected.shape[0]
+    inner = heads * vdim
+    if projected.dim() != 2 or projected.shape[1] < 2 * heads * dim + 2 * inner or projected.stride(1) != 1 or projected.dtype != out_dtype \
+            or decay.dtype != torch.float32 or decay.numel() != heads or state.dtype != torch.float32 or state.stride(-1) != 1 \
+            or state.shape[-1] < heads * dim * vdim or state_slots.numel() < R or positions.numel() < R:
+        raise ValueError("retention_decode: projected [R, q | k | v | g] in the compute dtype, decay float32 [heads], the state float32 "
+                         "[seats, >= heads dim vdim], a seat and a position per row")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise ValueError("inv_freq must be float32 [rot_dims / 2]")
+    y = into if into is not None else torch.empty((R, inner), dtype=out_dtype, device=projected.device)
+    if tuple(y.shape) != (R, inner) or y.dtype != out_dtype or y.stride(1) != 1:
+        raise ValueError("retention_decode: the rows go to [R, heads vdim] in the compute dtype with unit column stride")
+    _run(_core(), "fe_retention_decode", _ptr(projected), _c_ll(projected.stride(0)), _ptr(positions), _ptr(inv_freq),
+         _c_int(rot_dims if inv_freq is not None else 0), _c_float(key_scale), _ptr(decay), _ptr(state), _c_ll(state.stride(0)),
+         _ptr(state_slots), _ptr(y), _c_ll(y.stride(0)), _c_float(eps), _c_float(scale), _c_int(R), _c_int(heads), _c_int(dim),
+         _c_int(vdim), _c_int(state.shape[0]), _c_int(_code(out_dtype)), _stream())
+    return y
+
+
 # ---- attention over a cached latent ------------------------------------------------------------------------------
 def batched_linear(x, w, token_major=False):
     """x [B, M, K] (a view with any row and batch strides, unit stride along K) times w [B, N, K]^T, one small matrix a

@@ -74,6 +74,10 @@ class RetentionMixer(Mixer):
         H, d, dv = self.heads, self.dim, self.vdim
         state = ctx.groups[entry.cache_group].state(entry.cache_slot)        # [seats, H d dv] float32
         inv_freq, decay = self.tables(projected.device)
+        if ctx.max_q_len == 1:
+            # a step of one token a request: rotation, recurrence, head norm and gate in one kernel
+            return ops.retention_decode(projected, H, d, dv, ctx.positions, inv_freq, self.rot_dims, d ** -0.5, decay, state,
+                                        ctx.state_slots, self.eps, ctx.dtype, scale=scale, into=out)
         # queries and keys, rotated, the keys scaled: float32 from here on
         qk = ops.rotate_heads(projected, 2 * H, d, ctx.positions, inv_freq, self.rot_dims, ((H, 1.0), (H, d ** -0.5)))
         values = projected[:, 2 * H * d:2 * H * d + H * dv]

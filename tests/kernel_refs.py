@@ -334,6 +334,17 @@ def retention_scan(qk, values, decay, state, state_slots, cu_q, heads, dim, vdim
     return out.view(T, heads * vdim)
 
 
+def retention_decode(projected, heads, dim, vdim, positions, inv_freq, rot_dims, key_scale, decay, state, state_slots, eps, out_dtype,
+                     scale=1.0, into=None):
+    """One token a request: rotation, recurrence, head norm and gate (the three references above, one after the other)."""
+    R = projected.shape[0]
+    qk = rotate_heads(projected, 2 * heads, dim, positions, inv_freq, rot_dims, ((heads, 1.0), (heads, key_scale)))
+    at = 2 * heads * dim
+    cu = torch.arange(R + 1, dtype=torch.int32, device=projected.device)
+    o = retention_scan(qk, projected[:, at:at + heads * vdim], decay, state, state_slots, cu, heads, dim, vdim)
+    return head_rmsnorm_gate(o, None, projected[:, at + heads * vdim:at + 2 * heads * vdim], eps, heads, out_dtype, scale=scale, into=into)
+
+
 def mingru_scan(zxg, bias, state, state_slots, cu_q, width, out_dtype, max_q_len=0):
     """zxg [T, 3 width] float32 (z | x | g before their biases and activations).  z = sigmoid(. + b_z), u = . + b_x,
     c = u + 1/2 where u >= 0 else sigmoid(u), S <- (1 - z) S + z c from the seat's kept S (zeros for a seat below 0),

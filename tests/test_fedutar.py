@@ -560,6 +560,38 @@ def test_recurrence_in_blocks_of_tokens_against_the_walk(value_dtype, heads, dim
     assert (walked.cpu() - want).abs().max() <= 2e-5 * scale and (walked_state.cpu() - want_state).abs().max() <= 2e-5 * want_state.abs().max()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,dim,vdim,decay,rot", [(2, 64, 128, [0.97, 1.0], 32), (3, 24, 40, [0.5, 0.999, 0.9], 24), (1, 130, 72, [0.99], 0),
+                                                      (2, 10, 300, [0.0, 0.98], 4), (5, 8, 6, [0.9] * 5, 8)])
+def test_one_token_a_request_in_one_kernel(dtype, heads, dim, vdim, decay, rot):
+    """The decode kernel (rotation, recurrence, head norm, gate) against the three reference operations one after the other:
+    kept and absent seats, rows and destination inside wider buffers, sizes that are multiples of nothing, an output scale."""
+    import flexengine_b200.ops as ops
+    device, dt = "cuda:0", getattr(torch, dtype)
+    R, per, inner = 7, heads * dim * vdim, heads * vdim
+    g = torch.Generator().manual_seed(9)
+    projected = (torch.randn(R, 2 * heads * dim + 2 * inner + 5, generator=g) * 0.7).to(dt)
+    state = torch.randn(9, per + 2, generator=g)
+    seats = torch.tensor([3, -1, 0, 8, 5, -1, 1], dtype=torch.int32)
+    positions = torch.tensor([0, 1, 77, 1000, 12345, 3, 64], dtype=torch.int32)
+    w = torch.tensor(decay, dtype=torch.float32)
+    inv_freq = None
+    if rot:
+        inv_freq = torch.pow(torch.tensor(10000.0, dtype=F64), -2.0 * torch.arange(rot // 2, dtype=F64) / rot).float()
+    want_state = state.clone()
+    want = kernel_refs.retention_decode(projected, heads, dim, vdim, positions, inv_freq, rot, dim ** -0.5, w, want_state, seats, 1e-6,
+                                        torch.float32 if dtype == "float32" else dt, scale=1.3)
+    wide = torch.zeros(R, inner + 11, dtype=dt, device=device)
+    got_state = state.to(device)
+    ops.retention_decode(projected.to(device), heads, dim, vdim, positions.to(device), None if inv_freq is None else inv_freq.to(device), rot,
+                         dim ** -0.5, w.to(device), got_state, seats.to(device), 1e-6, dt, scale=1.3, into=wide[:, 3:3 + inner])
+    assert (got_state.cpu() - want_state).abs().max() <= 2e-6 * want_state.abs().max()
+    bar = 2e-5 if dtype == "float32" else 1.6e-2
+    assert (wide[:, 3:3 + inner].float().cpu() - want.float()).abs().max() <= bar * want.float().abs().max()
+    assert float(wide[:, :3].abs().max()) == 0.0 and float(wide[:, 3 + inner:].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("device,dtype", CASES)
 @pytest.mark.parametrize("shape", [((4, 2, 16, 24, (0.3, 5)), (3, 16, 8, [0.9, 0.95, 0.99], 8), 1.2, 0.9),
                                    ((1, 1, 48, 40, None), (1, 40, 24, [0.98], 20), 1.0, 0.5),
