@@ -1,1 +1,1 @@
-from . import fedutar, fuvozen, fuvuvik, qwen2  # noqa: F401  (register Fedutar, Fuvozen, Fuvuvik and Qwen2ForCausalLM)
+from . import fedutar, fuvozen, fuvuvik, qwen2, rikolix  # noqa: F401  (register Fedutar, Fuvozen, Fuvuvik, Rikolix and Qwen2ForCausalLM)

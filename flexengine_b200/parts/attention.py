@@ -104,18 +104,31 @@ class GatedAttentionMixer(Mixer):
     ``gate`` "head": every head's output is multiplied by sigmoid(w_g,h . x), x the rows the projections read; "element":
     every entry of the concatenated heads by the sigmoid of its own projection of x (``heads * vdim`` gate rows).  The value size may differ
     from the query/key size: the cache and the attention kernels run at ``head`` = the larger, in steps of 16, the
-    smaller padded with zeros (scores and outputs are the same).  No biases.
+    smaller padded with zeros (scores and outputs are the same).  ``gate`` "none": the heads go to the output projection as
+    they are.  No biases.
+    ``norm_scope`` "all" (with ``norm_weights``): instead of a norm per head, the whole query projection (all heads at once)
+    goes through one RMS norm with a weight of ``heads * dim`` numbers, and the whole key projection through one with
+    ``kv_heads * dim``; this norm comes BEFORE the rotation.
+    ``rot_pairs`` "interleaved": entry 2i turns with 2i + 1 instead of i with i + rot_dims/2.
+    ``rotate_values``: the value of position j turns by j over all ``vdim`` entries (pairs laid out as ``rot_pairs`` says,
+    pair m by j * rot_base^(-2m/vdim)) before it is cached, and a head's output at position i is turned back by i.
+    ``weights`` "sigmoid": the weight of a visible key is sigmoid(score * scale + b_head) with a learned number per head
+    (``score_bias``), not normalised over the keys.
 
     q, k, v and the head gates are one product; convolution, rotation, unit norm and the cache write are one kernel;
     angles, norms, scores and softmax are float32."""
 
     MASKS = ("full", "window", "chunk")
-    GATES = ("head", "element")
+    GATES = ("head", "element", "none")
+    NORM_SCOPES = ("head", "all")
+    ROT_PAIRS = ("halves", "interleaved")
+    WEIGHTS = ("softmax", "sigmoid")
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, rot_base: float = 10000.0,
                  rot_dims: int = 0, conv: int = 0, qk_norm: bool = False, eps: float = 1e-6, mask: str = "full", mask_size: int = 0,
                  sink: bool = False, conv_group: int = -1, conv_slot: int = -1, norm_weights: bool = False, temp_coef: float = 0.0,
-                 temp_every: int = 1, gate: str = "head"):
+                 temp_every: int = 1, gate: str = "head", norm_scope: str = "head", rot_pairs: str = "halves", rotate_values: bool = False,
+                 weights: str = "softmax"):
         if heads % kv_heads:
             raise ValueError("Invalid GQA head ratio")
         if mask not in self.MASKS or (mask != "full" and mask_size <= 0):
@@ -131,6 +144,24 @@ class GatedAttentionMixer(Mixer):
             raise ValueError(f"gate {gate!r}: known gates are {', '.join(self.GATES)}")
         if self.norm_weights and not self.qk_norm:
             raise ValueError("norm weights need the query/key norm")
+        if norm_scope not in self.NORM_SCOPES or rot_pairs not in self.ROT_PAIRS or weights not in self.WEIGHTS:
+            raise ValueError(f"norm_scope {norm_scope!r} / rot_pairs {rot_pairs!r} / weights {weights!r}: known are "
+                             f"{self.NORM_SCOPES}, {self.ROT_PAIRS} and {self.WEIGHTS}")
+        self.norm_scope, self.rot_pairs, self.rotate_values, self.weights = norm_scope, rot_pairs, bool(rotate_values), weights
+        # what the second preparation kernel does (a norm over the whole projection, neighbouring pairs, turned values) and
+        # what only the first one does (convolutions, a norm per head, the query temperature) do not meet in one layer
+        self.wide_prepare = norm_scope == "all" or rot_pairs == "interleaved" or self.rotate_values
+        if self.wide_prepare and (self.conv > 0 or self.temp_coef != 0.0 or (self.qk_norm and norm_scope == "head")):
+            raise ValueError("a norm over the whole projection, neighbouring rotation pairs or turned values go with neither a "
+                             "convolution, nor a norm per head, nor a query temperature")
+        if norm_scope == "all" and not self.norm_weights:
+            raise ValueError("the norm over the whole projection has weights")
+        if self.rotate_values and self.vdim % 2:
+            raise ValueError("values turn in pairs: vdim must be even")
+        if weights == "sigmoid" and self.sink:
+            raise ValueError("a sink belongs to a softmax")
+        self.score_bias = None
+        self._inv_freq_v = {}
         if self.temp_every < 1:
             raise ValueError("temp_every must be positive")
         self.q_norm_weight = self.k_norm_weight = None
@@ -149,7 +180,7 @@ class GatedAttentionMixer(Mixer):
 
     @property
     def gate_width(self) -> int:
-        return self.heads if self.gate == "head" else self.heads * self.vdim
+        return {"head": self.heads, "element": self.heads * self.vdim, "none": 0}[self.gate]
 
     @property
     def input_width(self) -> int:
@@ -167,8 +198,11 @@ class GatedAttentionMixer(Mixer):
         if self.conv > 0:
             shapes["conv.weight"] = ((self.channels, self.conv), "vector")
         if self.norm_weights:
-            shapes["q_norm.weight"] = ((self.dim,), "vector")
-            shapes["k_norm.weight"] = ((self.dim,), "vector")
+            every = self.norm_scope == "all"
+            shapes["q_norm.weight"] = ((self.heads * self.dim if every else self.dim,), "vector")
+            shapes["k_norm.weight"] = ((self.kv_heads * self.dim if every else self.dim,), "vector")
+        if self.weights == "sigmoid":
+            shapes["score_bias"] = ((self.heads,), "vector")
         return shapes
 
     def bind(self, tensors: dict) -> None:
@@ -190,6 +224,15 @@ class GatedAttentionMixer(Mixer):
             self._inv_freq[key] = table.to(torch.float32).to(device).contiguous()
         return self._inv_freq[key]
 
+    def value_inverse_frequencies(self, device):
+        """The values' rotation: pair m of ``vdim`` / 2 turns by position * rot_base^(-2m/vdim)."""
+        key = str(device)
+        if key not in self._inv_freq_v:
+            m = torch.arange(self.vdim // 2, dtype=torch.float64)
+            table = torch.pow(torch.tensor(self.rot_base, dtype=torch.float64), -2.0 * m / self.vdim)
+            self._inv_freq_v[key] = table.to(torch.float32).to(device).contiguous()
+        return self._inv_freq_v[key]
+
     def forward(self, ctx, h, entry):
         projected = ctx.ops.linear(h, self.qkvg_weight)                      # [T, channels + gates]
         return ctx.ops.linear(self.mix(ctx, projected, entry), self.o_weight)
@@ -208,17 +251,43 @@ class GatedAttentionMixer(Mixer):
             more.update(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight)
         if self.temp_coef != 0.0:
             more.update(temp=(self.temp_coef, self.temp_every))
-        queries = ops.qkv_conv_rope_norm_cache(
-            projected, self._conv_by_tap, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
-            self.inverse_frequencies(projected.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
-            k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size, **more)
+        turned = self.value_inverse_frequencies(projected.device) if self.rotate_values else None
+        if self.wide_prepare:
+            queries = ops.qkv_norm_rope_cache(
+                projected, self.q_norm_weight, self.k_norm_weight, self.eps, ctx.positions,
+                self.inverse_frequencies(projected.device) if self.rot_dims else None, self.rot_dims, self.rot_pairs, turned,
+                slot_mapping, k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size)
+        else:
+            queries = ops.qkv_conv_rope_norm_cache(
+                projected, self._conv_by_tap, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
+                self.inverse_frequencies(projected.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
+                k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size, **more)
         # one int says what a query sees: 0 every earlier key, w > 0 the last w, -c < 0 its own chunk of c positions
         visibility = {"full": 0, "window": self.mask_size, "chunk": -self.mask_size}[self.mask]
-        mixed = ops.paged_attention(queries, k_cache, v_cache, group.block_table, ctx, self.heads, self.kv_heads, self.head,
-                                    group.page_size, self.scale, visibility, sink=self.sink)
+        if self.weights == "sigmoid":
+            mixed = ops.paged_attention(queries, k_cache, v_cache, group.block_table, ctx, self.heads, self.kv_heads, self.head,
+                                        group.page_size, self.scale, visibility, weights="sigmoid", head_bias=self.score_bias)
+        else:
+            mixed = ops.paged_attention(queries, k_cache, v_cache, group.block_table, ctx, self.heads, self.kv_heads, self.head,
+                                        group.page_size, self.scale, visibility, sink=self.sink)
+        head = self.head
+        if self.rotate_values:
+            # every head's sum turned back by the query's position; the padding of the kernels' head size goes on the way
+            if self.gate == "none":
+                return ops.unrotate_heads(mixed, ctx.positions, turned, self.heads, head, self.vdim, self.rot_pairs, scale=scale, out=out)
+            mixed, head = ops.unrotate_heads(mixed, ctx.positions, turned, self.heads, head, self.vdim, self.rot_pairs), self.vdim
+        elif self.gate == "none":
+            rows = mixed if head == self.vdim else mixed.view(-1, self.heads, head)[:, :, :self.vdim].reshape(-1, self.inner_width)
+            if out is None and scale == 1.0:
+                return rows
+            rows = rows if scale == 1.0 else rows * scale
+            if out is None:
+                return rows
+            out.copy_(rows)
+            return out
         if self.gate == "head" and out is None and scale == 1.0:
-            return ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim)
-        return ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim, per_element=self.gate == "element",
+            return ops.head_gate(mixed, projected, self.channels, self.heads, head, self.vdim)
+        return ops.head_gate(mixed, projected, self.channels, self.heads, head, self.vdim, per_element=self.gate == "element",
                              scale=scale, out=out)
 
 

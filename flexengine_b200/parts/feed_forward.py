@@ -58,24 +58,38 @@ class SwiGLU(FeedForward):
         return ctx.ops.linear(act, self.down_weight, follow=follow, upcoming=upcoming)
 
 
-class XieluMlp(FeedForward):
-    """down( act(up(h)) ) with the two-sided activation xIELU of two learned numbers p, q:
-    z > 0: softplus(p) z^2 + z/2;   z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+class ActivatedMlp(FeedForward):
+    """down( act(up(h)) ), one matrix up, one down, no gate.  ``activation``:
+    "xielu": two-sided, with two learned numbers p, q (``act``): z > 0: softplus(p) z^2 + z/2;
+             z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;
+    "relu2": the square of relu(z)."""
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    ACTIVATIONS = ("xielu", "relu2")
+    takes_prenormed = False
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu"):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.activation = activation
         self.up_weight = self.down_weight = self.act = None
 
     def parameter_shapes(self) -> dict:
         h, i = self.hidden_size, self.intermediate_size
-        return {"up.weight": ((i, h), "matrix"), "down.weight": ((h, i), "matrix"), "act": ((2,), "vector")}
+        shapes = {"up.weight": ((i, h), "matrix"), "down.weight": ((h, i), "matrix")}
+        if self.activation == "xielu":
+            shapes["act"] = ((2,), "vector")
+        return shapes
 
     def reads_first(self):
         return self.up_weight
 
     def forward(self, ctx, h):
         ops = ctx.ops
-        return ops.linear(ops.activation(ops.linear(h, self.up_weight), "xielu", self.act), self.down_weight)
+        if self.activation == "xielu":
+            return ops.linear(ops.activation(ops.linear(h, self.up_weight), "xielu", self.act), self.down_weight)
+        # the product's epilogue squares where a kernel of this package takes the product; else product, then activation
+        return ops.linear(ops.linear_activated(h, self.up_weight, self.activation), self.down_weight)
 
 
 class RoutedExperts(FeedForward):
@@ -88,13 +102,20 @@ class RoutedExperts(FeedForward):
     rows (``ops.routed_experts``): no count ever comes back to the host, so the step can be a CUDA graph."""
 
     ROUTERS = ("softmax_all", "softmax_chosen")
-    ACTIVATIONS = ("silu", "clamped")
+    ACTIVATIONS = ("silu", "clamped", "relu2")
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, scale: float = 1.0, shared_size: int = 0,
-                 router: str = "softmax_all", activation: str = "silu", limit: float = 0.0):
+                 router: str = "softmax_all", activation: str = "silu", limit: float = 0.0, identity: int = 0,
+                 correction: bool = False, groups: int = 1, keep: int = 1):
         """``router`` "softmax_all": as above; "softmax_chosen": the ``top`` largest logits are chosen and the weights are
         the softmax over the chosen logits only.  ``activation`` "silu": as above; "clamped": with g = min(gate h, limit)
-        and u = clamp(up h, -limit, limit) an expert is down( g * sigmoid(1.702 g) * (u + 1) )."""
+        and u = clamp(up h, -limit, limit) an expert is down( g * sigmoid(1.702 g) * (u + 1) ); "relu2": an expert has no
+        gate and is down( relu(up h)^2 ).
+        ``identity``: the router has that many further outputs, after the experts', that stand for experts which return
+        their input (times the weight); they have no tensors.  ``correction``: a learned number per router output is added
+        to the scores for the choice only; the weights are the uncorrected scores.  ``groups``, ``keep``: the router's
+        outputs form ``groups`` equal groups of neighbours, a group's score is its largest (corrected) score, and only
+        outputs of the ``keep`` best groups can be chosen."""
         self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
         self.expert_size, self.scale, self.shared_size = int(expert_size), float(scale), int(shared_size)
         if router not in self.ROUTERS or activation not in self.ACTIVATIONS:
@@ -102,13 +123,26 @@ class RoutedExperts(FeedForward):
         if activation == "clamped" and not limit > 0.0:
             raise ValueError("the clamped activation needs a positive limit")
         self.router, self.activation, self.limit = router, activation, float(limit)
-        self.router_weight = self.experts_gate_up_weight = self.experts_down_weight = None
+        self.identity, self.correction, self.groups, self.keep = int(identity), bool(correction), int(groups), int(keep)
+        outputs = self.experts + self.identity
+        if self.identity < 0 or self.groups < 1 or outputs % self.groups or not (1 <= self.keep <= self.groups):
+            raise ValueError("the groups must share the router's outputs out equally, and 1 <= keep <= groups")
+        if (self.correction or self.groups > 1) and router != "softmax_all":
+            raise ValueError("a correction and groups go with the softmax over all router outputs")
+        if self.shared_size and activation == "relu2":
+            raise ValueError("the shared expert is a gated one")
+        self.router_weight = self.router_correction = self.experts_gate_up_weight = self.experts_up_weight = self.experts_down_weight = None
         self.shared_gate_up_weight = self.shared_down_weight = None
 
     def parameter_shapes(self) -> dict:
         h, e, f = self.hidden_size, self.experts, self.expert_size
-        shapes = {"router.weight": ((e, h), "float32"), "experts.gate_up.weight": ((e * 2 * f, h), "matrix"),
-                  "experts.down.weight": ((e * h, f), "matrix")}
+        shapes = {"router.weight": ((e + self.identity, h), "float32"), "experts.down.weight": ((e * h, f), "matrix")}
+        if self.activation == "relu2":
+            shapes["experts.up.weight"] = ((e * f, h), "matrix")
+        else:
+            shapes["experts.gate_up.weight"] = ((e * 2 * f, h), "matrix")
+        if self.correction:
+            shapes["router.correction"] = ((e + self.identity,), "vector")
         if self.shared_size:
             shapes["shared.gate_up.weight"] = ((2 * self.shared_size, h), "matrix")
             shapes["shared.down.weight"] = ((h, self.shared_size), "matrix")
@@ -124,7 +158,14 @@ class RoutedExperts(FeedForward):
         shared = None
         if self.shared_size:
             shared = ops.linear(ops.linear_swiglu(h, self.shared_gate_up_weight, self.shared_size), self.shared_down_weight)
-        gate_up, down = self.experts_gate_up_weight.view(e, 2 * f, d), self.experts_down_weight.view(e, d, f)
+        down = self.experts_down_weight.view(e, d, f)
+        if self.activation == "relu2" or self.identity or self.correction or self.groups > 1:
+            chosen, weights = ops.route_top(logits, self.top, self.scale, over_chosen=self.router == "softmax_chosen",
+                                            correction=self.router_correction, groups=(self.groups, self.keep))
+            first = self.experts_up_weight.view(e, f, d) if self.activation == "relu2" else self.experts_gate_up_weight.view(e, 2 * f, d)
+            return ops.routed_experts(h, chosen, weights, first, down, shared, activation=self.activation, limit=self.limit,
+                                      identity=self.identity)
+        gate_up = self.experts_gate_up_weight.view(e, 2 * f, d)
         if self.router == "softmax_all" and self.activation == "silu":
             chosen, weights = ops.route_top(logits, self.top, self.scale)
             return ops.routed_experts(h, chosen, weights, gate_up, down, shared)
@@ -134,5 +175,6 @@ class RoutedExperts(FeedForward):
 
 register_feed_forward("swiglu", SwiGLU)
 register_feed_forward("gated_mlp", SwiGLU)
-register_feed_forward("xielu_mlp", XieluMlp)
+register_feed_forward("xielu_mlp", ActivatedMlp)
+register_feed_forward("mlp", ActivatedMlp)
 register_feed_forward("routed_experts", RoutedExperts)

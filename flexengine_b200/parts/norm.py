@@ -24,13 +24,22 @@ class PostNormed:
 
 
 class RMSNorm(Norm):
-    def __init__(self, hidden_size: int, eps: float):
+    """``unit_offset``: the checkpoint stores the weight around zero and the norm multiplies by (1 + w).  The sum is taken
+    once, in float32, when the weights are bound; the kernels see a plain weight."""
+
+    def __init__(self, hidden_size: int, eps: float, unit_offset: bool = False):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
+        self.unit_offset = bool(unit_offset)
         self.weight = None
 
     def parameter_shapes(self) -> dict:
         return {"weight": ((self.hidden_size,), "vector")}
+
+    def bind(self, tensors: dict) -> None:
+        super().bind(tensors)
+        if self.unit_offset:
+            self.weight = self.weight.to(torch.float32) + 1.0
 
     def forward(self, ctx, residual, delta, rows=None, upcoming=None):
         if isinstance(delta, PostNormed):

@@ -134,9 +134,11 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     return qkv
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False,
+                    weights="softmax", head_bias=None):
     """``window`` > 0: the last ``window`` keys; < 0: the earlier keys of the query's chunk of -window positions.
-    ``sink``: 1 is added to the softmax's denominator."""
+    ``sink``: 1 is added to the softmax's denominator.  ``weights`` "sigmoid": a visible key weighs
+    sigmoid(score + head_bias[head]), not normalised over the keys."""
     T = qkv.shape[0]
     chunk, window = (-window, 0) if window < 0 else (0, window)
     out = torch.zeros(T, nq * d, dtype=qkv.dtype, device=qkv.device)
@@ -164,7 +166,9 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         vh = v.repeat_interleave(ratio, dim=1)
         scores = torch.einsum("qhd,thd->hqt", q, kh) * scale
         scores = scores.masked_fill(~visible[None], float("-inf"))
-        if sink:
+        if weights == "sigmoid":
+            w = torch.sigmoid(scores if head_bias is None else scores + head_bias.float()[:, None, None])
+        elif sink:
             top = torch.clamp(scores.max(dim=-1, keepdim=True).values, min=0.0)
             e = torch.exp(scores - top)
             w = e / (e.sum(dim=-1, keepdim=True) + torch.exp(-top))
@@ -280,6 +284,69 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
         k_cache[page, :, off] = kp[keep]
         v_cache[page, :, off] = vp[keep]
     return queries.view(T, heads * head)
+
+
+def _turn(x, positions, inv_freq, dims, pairs, sign=1.0):
+    """x [T, heads, n]: the first ``dims`` entries of every head turn by sign * position * inv_freq."""
+    ang = sign * positions.float()[:, None] * inv_freq.float()[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    y = x.clone()
+    if pairs == "interleaved":
+        a, b = x[..., 0:dims:2], x[..., 1:dims:2]
+        y[..., 0:dims:2] = a * cos - b * sin
+        y[..., 1:dims:2] = b * cos + a * sin
+    else:
+        half = dims // 2
+        a, b = x[..., :half], x[..., half:dims]
+        y[..., :half] = a * cos - b * sin
+        y[..., half:dims] = b * cos + a * sin
+    return y
+
+
+def qkv_norm_rope_cache(projected, q_weight, k_weight, eps, positions, inv_freq, rot_dims, pairs, value_inv_freq, slot_mapping,
+                        k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+    """projected [T, >= channels] holds q | k | v.  One RMS norm over the whole query projection and one over the whole key
+    projection (weights of their full widths; None: no norm), then the rotation of the first ``rot_dims`` entries of every
+    query and key head, the values turned over all ``vdim`` entries (``value_inv_freq`` None: as they are), keys and values
+    into the cache and the queries out, padded with zeros to ``head`` entries a head."""
+    T = projected.shape[0]
+    qw, kw = heads * dim, kv_heads * dim
+    u = projected.float()
+    q, k, v = u[:, :qw], u[:, qw:qw + kw], u[:, qw + kw:qw + kw + kv_heads * vdim]
+    if q_weight is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(dim=-1, keepdim=True) + eps) * q_weight.float()
+        k = k * torch.rsqrt(k.pow(2).mean(dim=-1, keepdim=True) + eps) * k_weight.float()
+    q, k, v = q.reshape(T, heads, dim), k.reshape(T, kv_heads, dim), v.reshape(T, kv_heads, vdim)
+    if inv_freq is not None and rot_dims > 0:
+        q, k = _turn(q, positions, inv_freq, rot_dims, pairs), _turn(k, positions, inv_freq, rot_dims, pairs)
+    if value_inv_freq is not None:
+        v = _turn(v, positions, value_inv_freq, vdim, pairs)
+    dt = projected.dtype
+    queries = torch.zeros(T, heads, head, dtype=dt, device=u.device)
+    queries[..., :dim] = q.to(dt)
+    if slot_mapping is not None:
+        slots = slot_mapping.long()
+        keep = slots >= 0
+        page, off = slots[keep] // page_size, slots[keep] % page_size
+        kp = torch.zeros(T, kv_heads, head, dtype=dt, device=u.device)
+        vp = torch.zeros(T, kv_heads, head, dtype=dt, device=u.device)
+        kp[..., :dim] = k.to(dt)
+        vp[..., :vdim] = v.to(dt)
+        k_cache[page, :, off] = kp[keep]
+        v_cache[page, :, off] = vp[keep]
+    return queries.view(T, heads * head)
+
+
+def unrotate_heads(mixed, positions, inv_freq, heads, head, vdim, pairs, scale=1.0, out=None):
+    """[T, heads vdim]: the first ``vdim`` entries of every head of ``mixed`` [T, heads head] turned back by the position
+    (pair m by -position * inv_freq[m]), times ``scale``."""
+    T = mixed.shape[0]
+    rows = _turn(mixed.float().view(T, heads, head)[..., :vdim], positions, inv_freq, vdim, pairs, sign=-1.0) * scale
+    rows = rows.reshape(T, heads * vdim).to(mixed.dtype)
+    if out is None:
+        return rows
+    out.copy_(rows)
+    return out
 
 
 def head_gate(mixed, projected, offset, heads, head, vdim, per_element=False, scale=1.0, out=None):
@@ -444,9 +511,15 @@ def activation(x, kind, params=None):
         p, q = params.float()
         ap, an = torch.log1p(torch.exp(p)), 0.5 + torch.log1p(torch.exp(q))
         y = torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.exp(torch.clamp(z, max=0.0)) - 1.0 - z) + 0.5 * z)
+    elif kind == "relu2":
+        y = torch.relu(z) ** 2
     else:
         raise ValueError(kind)
     return y.to(x.dtype)
+
+
+def linear_activated(x, w, kind):
+    return activation(linear(x, w), kind)
 
 
 def wkv_recurrence(r, k, v, decay_logits, w0, u, state, state_slots, cu_q, heads, dim):
@@ -509,6 +582,8 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
     queries = torch.zeros(T, heads, row, dtype=torch.float32, device=q.device)
     queries[:, :, :rank] = q_latent.float().transpose(0, 1)
     queries[:, :, rank:rank + rot_dim] = turn(qf[:, :, dim:])
+    if down is None:                             # a layer that reads another layer's latents: queries only
+        return queries.view(T, heads * row).to(q.dtype)
     latent = down.float()[:, :rank]
     latent = latent * torch.rsqrt(latent.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight.float()
     cached = torch.zeros(T, row, dtype=torch.float32, device=q.device)
@@ -522,7 +597,23 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
 
 
 # ---- routed feed-forward ------------------------------------------------------------------------------
-def route_top(logits, top, scale, over_chosen=False):
+def route_top(logits, top, scale, over_chosen=False, correction=None, groups=(1, 1)):
+    """``correction`` (float32, one number per router output) is added to the scores for the choice only; ``groups`` =
+    (count, keep): only outputs of the ``keep`` groups (of ``count`` equal groups of neighbours) with the largest corrected
+    score can be chosen.  Ties go to the lower index."""
+    count, keep = groups
+    if correction is not None or count > 1:
+        scores = torch.softmax(logits.float(), dim=-1)
+        choice = scores if correction is None else scores + correction.float()
+        T, E = choice.shape
+        if count > 1:
+            best = choice.view(T, count, E // count).max(dim=-1).values
+            order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
+            kept = torch.zeros(T, count, dtype=torch.bool, device=choice.device)
+            kept.scatter_(1, order, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(E // count, dim=1), float("-inf"))
+        picked = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+        return picked.to(torch.int32), (scores.gather(1, picked) * scale).float()
     if over_chosen:
         best = torch.topk(logits.float(), top, dim=-1)
         return best.indices.to(torch.int32), (torch.softmax(best.values, dim=-1) * scale).float()
@@ -531,15 +622,26 @@ def route_top(logits, top, scale, over_chosen=False):
     return best.indices.to(torch.int32), (best.values * scale).float()
 
 
-def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0):
+def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0, identity=0):
+    """``activation`` "relu2": ``gate_up`` is [experts, F, H], an expert is down(relu(up h)^2).  ``identity``: choices from
+    ``experts`` on stand for experts that return their input."""
     T, D = h.shape
     f = down.shape[2]
+    experts = down.shape[0]
     total = torch.zeros(T, D, dtype=torch.float32, device=h.device)
     hf = h.float()
     for slot in range(chosen.shape[1]):                   # a token's experts are added in the order they were chosen
         for e in chosen[:, slot].unique().tolist():
             rows = (chosen[:, slot] == e).nonzero().flatten()
+            if e >= experts:
+                if e < experts + identity:
+                    total[rows] += weights[rows, slot, None] * hf[rows]
+                continue
             gu = hf[rows] @ gate_up[e].float().T
+            if activation == "relu2":
+                act = (torch.relu(gu) ** 2).to(h.dtype).float()
+                total[rows] += weights[rows, slot, None] * (act @ down[e].float().T)
+                continue
             g, u = gu[:, :f], gu[:, f:]
             if activation == "clamped":
                 g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
