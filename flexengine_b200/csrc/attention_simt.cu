@@ -6,7 +6,8 @@
 // inference/attention/paged.py:50-70).  Key t is visible to the query at position p iff t <= p
 // (and t > p - window when window > 0; t in the chunk of -window positions that holds p when window < 0)
 // (paged.py:31-32).  ``sink``: the softmax starts as if a key of score 0 and value 0 had been seen, which adds
-// 1 to its denominator.  Query head h reads key/value head
+// 1 to its denominator.  ``mode`` bit 1 (bit 0 is the sink): no softmax; the weight of a visible key is
+// sigmoid(score + head_bias[h]), not normalised over the keys.  Query head h reads key/value head
 // h / (nq / nkv) (paged.py:29-30).  Because the blocks are aligned to position 0 and taken in
 // order, the result for a query does not depend on how its request was cut into steps.
 //
@@ -25,7 +26,7 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
                                             int bt_stride, const int* __restrict__ cu_q,
                                             const int* __restrict__ q_start, const int* __restrict__ token_req,
                                             int T_tokens, int nq, int nkv, int d, int ps, int num_pages, float scale,
-                                            int window, int sink, int* __restrict__ status) {
+                                            int window, int mode, const float* __restrict__ head_bias, int* __restrict__ status) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float q_smem[];
@@ -42,6 +43,8 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
     for (int j = lane; j < d; j += 32) qs[j] = to_float(qp[j]);
     __syncwarp();
 
+    const bool sink = mode & 1, sigmoid = mode & 2;
+    const float bias = (sigmoid && head_bias) ? head_bias[h] : 0.f;
     float m = sink ? 0.f : -CUDART_INF_F, l = sink ? 1.f : 0.f;
     float acc[DPL];
 #pragma unroll
@@ -72,14 +75,21 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
                 s = dot * scale;
             }
         }
-        const float bm = warp_max(s);
-        if (bm == -CUDART_INF_F) continue;            // nothing visible in this block (bad pages only)
-        const float m_new = fmaxf(m, bm);
-        const float alpha = expf(m - m_new);           // exp(-inf) = 0 on the first block
-        const float p = valid ? expf(s - m_new) : 0.f;
-        l = l * alpha + warp_sum(p);
+        float p;
+        if (sigmoid) {
+            p = valid ? 1.f / (1.f + expf(-(s + bias))) : 0.f;
+            l = 1.f;                                   // the sum is not divided by anything
+        } else {
+            const float bm = warp_max(s);
+            if (bm == -CUDART_INF_F) continue;         // nothing visible in this block (bad pages only)
+            const float m_new = fmaxf(m, bm);
+            const float alpha = expf(m - m_new);       // exp(-inf) = 0 on the first block
+            p = valid ? expf(s - m_new) : 0.f;
+            l = l * alpha + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] *= alpha;
+            for (int i = 0; i < DPL; ++i) acc[i] *= alpha;
+            m = m_new;
+        }
         const int count = min(32, pos - kb + 1);
         for (int tt = 0; tt < count; ++tt) {
             const float pt = __shfl_sync(0xffffffffu, p, tt);
@@ -93,7 +103,6 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
                 }
             }
         }
-        m = m_new;
     }
     T* op = out + (size_t)tok * out_stride + (size_t)h * d;
     const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -108,7 +117,7 @@ template <typename T>
 static int launch_simt(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                        const void* vc, const int* block_table, int bt_stride, const int* cu_q, const int* q_start,
                        const int* token_req, int T_tokens, int nq, int nkv, int d, int ps, int num_pages,
-                       float scale, int window, int sink, int* status, cudaStream_t stream) {
+                       float scale, int window, int sink, const float* head_bias, int* status, cudaStream_t stream) {
     const int warps = 4;
     const long long total = (long long)T_tokens * nq;
     const int blocks = (int)((total + warps - 1) / warps);
@@ -116,7 +125,7 @@ static int launch_simt(const void* q, long long q_stride, void* out, long long o
 #define FE_LAUNCH_SIMT(DPL)                                                                                      \
     fe::launch(paged_attention_simt_kernel<T, DPL>, blocks, warps * 32, smem, stream,                                    \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kc, (const T*)vc, block_table, bt_stride, cu_q,   \
-        q_start, token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status)
+        q_start, token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, head_bias, status)
     if (d <= 32) FE_LAUNCH_SIMT(1);
     else if (d <= 64) FE_LAUNCH_SIMT(2);
     else if (d <= 128) FE_LAUNCH_SIMT(4);
@@ -131,7 +140,7 @@ extern "C" int fe_paged_attention_simt(const void* q, long long q_stride, void* 
                                        const void* kc, const void* vc, const int* block_table, int bt_stride,
                                        const int* cu_q, const int* q_start, const int* token_req, int T_tokens,
                                        int nq, int nkv, int d, int ps, int num_pages, float scale, int window,
-                                       int sink, int dtype, int* status, cudaStream_t stream) {
+                                       int sink, int dtype, int* status, const float* head_bias, cudaStream_t stream) {
     FE_REQUIRE(T_tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "paged_attention: bad head counts %d/%d", nq, nkv);
     FE_REQUIRE(d >= 16 && d <= 1024 && d % 16 == 0, "paged_attention: head size %d is not a multiple of 16 in [16, 1024]", d);
     FE_REQUIRE(ps > 0 && num_pages > 0, "paged_attention: bad page size or page count");
@@ -139,9 +148,9 @@ extern "C" int fe_paged_attention_simt(const void* q, long long q_stride, void* 
     if (T_tokens == 0) return 0;
     if (dtype == FE_F32)
         return launch_simt<float>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                  token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status, stream);
+                                  token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, head_bias, status, stream);
     if (dtype == FE_BF16)
         return launch_simt<bf16>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                 token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status, stream);
+                                 token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, head_bias, status, stream);
     FE_REQUIRE(false, "paged_attention: unknown dtype %d", dtype);
 }

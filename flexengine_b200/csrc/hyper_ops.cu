@@ -707,6 +707,177 @@ extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const
 }
 
 // ---------------------------------------------------------------------------------------------
+// Between the projection and the scores, second form: norms over whole projections, and values that turn.  ``proj`` [T, ld]
+// holds q | k | v as above.  One block per token:
+//   norm (q_weight, k_weight given): the token's whole query projection (all heads at once) is divided by its root mean
+//     square and multiplied by a weight of heads * dim numbers; the whole key projection likewise (kv_heads * dim);
+//   rotation (q, k), after the norm: the first ``rot`` entries of every head turn by position * inv_freq[i]; pairs are
+//     (2i, 2i + 1) when ``interleaved``, else (i, i + rot/2);
+//   values (v_inv_freq given): all ``vdim`` entries of every value head turn by position * v_inv_freq[m], pairs laid out
+//     the same way;
+//   q into ``q_out`` [T, heads * head], k and v into their cache slots [pages, kv_heads, ps, head], zeros beyond dim / vdim.
+// The token's row is staged in shared memory as floats; sines and cosines are worked out once a token, in float.
+namespace {
+
+// entry c of a head whose first ``dims`` entries turn: the entry after the turn.  ``at`` points at the head's first entry.
+__device__ __forceinline__ float turned_entry(const float* at, int c, int dims, int interleaved, const float* cosines,
+                                              const float* sines, float sign) {
+    const float v = at[c];
+    if (c >= dims) return v;
+    const int half = dims >> 1;
+    int i, partner;
+    bool second;
+    if (interleaved) { i = c >> 1; partner = c ^ 1; second = c & 1; }
+    else { second = c >= half; i = second ? c - half : c; partner = second ? c - half : c + half; }
+    const float other = at[partner], co = cosines[i], si = sign * sines[i];
+    return second ? fmaf(v, co, other * si) : fmaf(v, co, -other * si);
+}
+
+template <typename T>
+__global__ void qkv_norm_rope_cache_kernel(const T* __restrict__ proj, long long ld, const float* __restrict__ q_weight,
+                                           const float* __restrict__ k_weight, float eps, const int* __restrict__ positions,
+                                           const float* __restrict__ inv_freq, int rot, int interleaved,
+                                           const float* __restrict__ v_inv_freq, const int* __restrict__ slot_mapping,
+                                           T* __restrict__ kc, T* __restrict__ vc, T* __restrict__ q_out, int heads, int kv_heads,
+                                           int dim, int vdim, int head, int ps, long long num_slots, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ float staged[];
+    __shared__ float scratch[33];
+    const int tok = blockIdx.x;
+    const int qw = heads * dim, kw = kv_heads * dim, vw = kv_heads * vdim;
+    const int C = qw + kw + vw;
+    const int half = rot >> 1, vhalf = v_inv_freq ? vdim >> 1 : 0;
+    float* row = staged;                              // [C]
+    float* cosines = staged + C;                      // [half], then the sines [half]
+    float* sines = cosines + half;
+    float* vcos = sines + half;                       // [vhalf], then [vhalf]
+    float* vsin = vcos + vhalf;
+    const float pos = (float)positions[tok];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sines[i], &cosines[i]);
+    for (int i = threadIdx.x; i < vhalf; i += blockDim.x) sincosf(pos * v_inv_freq[i], &vsin[i], &vcos[i]);
+    const T* src = proj + (size_t)tok * ld;
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float v = to_float(src[c]);
+        row[c] = v;
+        if (c < qw) ssq = fmaf(v, v, ssq);
+        else if (c < qw + kw) ssk = fmaf(v, v, ssk);
+    }
+    if (q_weight) {
+        const float inv_q = rsqrtf(block_sum(ssq, scratch) / (float)qw + eps);
+        const float inv_k = rsqrtf(block_sum(ssk, scratch) / (float)kw + eps);
+        for (int c = threadIdx.x; c < qw + kw; c += blockDim.x)
+            row[c] *= c < qw ? inv_q * q_weight[c] : inv_k * k_weight[c - qw];
+    }
+    __syncthreads();
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (slot_mapping) {
+        const int slot = slot_mapping[tok];
+        if (slot >= 0) {
+            if (slot >= num_slots) {
+                if (threadIdx.x == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);
+            } else {
+                const long long page = slot / ps, off = slot % ps;
+                kdst = kc + ((page * kv_heads) * ps + off) * head;          // head 0; the next head is ps * head further
+                vdst = vc + ((page * kv_heads) * ps + off) * head;
+            }
+        }
+    }
+    T* qdst = q_out + (size_t)tok * heads * head;
+    const int per_token = heads + 2 * kv_heads;
+    for (int e = threadIdx.x; e < per_token * head; e += blockDim.x) {
+        const int hs = e / head, c = e - hs * head;
+        float v = 0.f;
+        if (hs < heads + kv_heads) {
+            if (c < dim) v = turned_entry(row + (size_t)hs * dim, c, rot, interleaved, cosines, sines, 1.f);
+            if (hs < heads) qdst[(size_t)hs * head + c] = from_float<T>(v);
+            else if (kdst) kdst[(size_t)(hs - heads) * ps * head + c] = from_float<T>(v);
+        } else if (vdst) {
+            const int index = hs - heads - kv_heads;
+            if (c < vdim) v = turned_entry(row + qw + kw + (size_t)index * vdim, c, vhalf * 2, interleaved, vcos, vsin, 1.f);
+            vdst[(size_t)index * ps * head + c] = from_float<T>(v);
+        }
+    }
+}
+
+// out[t, h, :vdim] = the first vdim entries of head h of mixed[t] turned BACK by the token's position (pair m by
+// -position * inv_freq[m]), times ``scale``; the padding of the attention kernels' head size is dropped on the way.
+template <typename T>
+__global__ void unrotate_heads_kernel(const T* __restrict__ mixed, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                      T* __restrict__ out, long long ldo, int heads, int head, int vdim, int interleaved, float scale) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ float trig[];                  // cos [vdim / 2], sin [vdim / 2]
+    const int tok = blockIdx.x, half = vdim >> 1;
+    const float pos = (float)positions[tok];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+    __syncthreads();
+    const T* src = mixed + (size_t)tok * heads * head;
+    T* dst = out + (size_t)tok * ldo;
+    for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+        const int h = e / half, i = e - h * half;
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_float(src[(size_t)h * head + a]), v = to_float(src[(size_t)h * head + b]);
+        const float co = trig[i], si = trig[half + i];
+        dst[(size_t)h * vdim + a] = from_float<T>((u * co + v * si) * scale);
+        dst[(size_t)h * vdim + b] = from_float<T>((v * co - u * si) * scale);
+    }
+}
+
+}  // namespace
+
+extern "C" int fe_qkv_norm_rope_cache(const void* proj, long long ld, const float* q_weight, const float* k_weight, float eps,
+                                      const int* positions, const float* inv_freq, int rot, int interleaved, const float* v_inv_freq,
+                                      const int* slot_mapping, void* kc, void* vc, void* q_out, int T, int heads, int kv_heads, int dim,
+                                      int vdim, int head, int ps, long long num_slots, int dtype, int* status, cudaStream_t stream) {
+    FE_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "qkv_norm_rope_cache: the norm weights come in pairs");
+    FE_REQUIRE(T >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && head >= dim && head >= vdim && head <= 1024,
+               "qkv_norm_rope_cache: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d head=%d", heads, kv_heads, dim, vdim, head);
+    FE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim && ps > 0 && (inv_freq != nullptr || rot == 0) && (v_inv_freq == nullptr || vdim % 2 == 0),
+               "qkv_norm_rope_cache: bad rotation or page size");
+    const long long C = (long long)(heads + kv_heads) * dim + (long long)kv_heads * vdim;
+    FE_REQUIRE(ld >= C, "qkv_norm_rope_cache: rows too short");
+    if (T == 0) return 0;
+    const size_t smem = ((size_t)C + rot + (v_inv_freq ? vdim : 0)) * sizeof(float);
+    FE_REQUIRE(smem <= 200 * 1024, "qkv_norm_rope_cache: a token's projections need %zu bytes of shared memory (limit 204800)", smem);
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "qkv_norm_rope_cache: unknown dtype %d", dtype);
+    const int threads = C >= 2048 ? 512 : 256;
+#define FE_LAUNCH_QKV_NORM(TYPE)                                                                                                        \
+    do {                                                                                                                                \
+        if (smem > 48 * 1024) {                                                                                                         \
+            cudaError_t err = cudaFuncSetAttribute(qkv_norm_rope_cache_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            FE_REQUIRE(err == cudaSuccess, "qkv_norm_rope_cache: %s", cudaGetErrorString(err));                                          \
+        }                                                                                                                               \
+        fe::launch(qkv_norm_rope_cache_kernel<TYPE>, T, threads, smem, stream, (const TYPE*)proj, ld, q_weight, k_weight, eps, positions, \
+                   inv_freq, rot, interleaved, v_inv_freq, slot_mapping, (TYPE*)kc, (TYPE*)vc, (TYPE*)q_out, heads, kv_heads, dim, vdim,    \
+                   head, ps, num_slots, status);                                                                                        \
+    } while (0)
+    if (dtype == FE_F32) FE_LAUNCH_QKV_NORM(float);
+    else FE_LAUNCH_QKV_NORM(bf16);
+#undef FE_LAUNCH_QKV_NORM
+    return fe_check_launch("qkv_norm_rope_cache");
+}
+
+extern "C" int fe_unrotate_heads(const void* mixed, const int* positions, const float* inv_freq, void* out, long long ldo, int T,
+                                 int heads, int head, int vdim, int interleaved, float scale, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && heads > 0 && vdim > 0 && vdim % 2 == 0 && head >= vdim && ldo >= (long long)heads * vdim && inv_freq != nullptr,
+               "unrotate_heads: bad sizes");
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "unrotate_heads: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const size_t smem = (size_t)vdim * sizeof(float);
+    const int threads = heads * vdim >= 2048 ? 512 : 256;
+    if (dtype == FE_F32)
+        fe::launch(unrotate_heads_kernel<float>, T, threads, smem, stream, (const float*)mixed, positions, inv_freq, (float*)out, ldo, heads,
+                   head, vdim, interleaved, scale);
+    else
+        fe::launch(unrotate_heads_kernel<bf16>, T, threads, smem, stream, (const bf16*)mixed, positions, inv_freq, (bf16*)out, ldo, heads,
+                   head, vdim, interleaved, scale);
+    return fe_check_launch("unrotate_heads");
+}
+
+// ---------------------------------------------------------------------------------------------
 // out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(gate) * scale: every head's output times its gate, the padding of the
 // attention kernels' head size dropped on the way.  The gate of entry c of head h is gates[t * ld + h] (one a head), or
 // gates[t * ld + h * vdim + c] with ``per_element``.  A row of out is ldo entries long (a view of a wider buffer).

@@ -38,13 +38,15 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q, const T* __restri
         trig[i] = c;
         trig[half + i] = s;
     }
-    const float* dr = down + (size_t)t * (rank + rot_dim);
+    // ``down`` null: a layer that reads the rows another layer cached; only the queries are made
+    const float* dr = down ? down + (size_t)t * (rank + rot_dim) : nullptr;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) ss += dr[j] * dr[j];
+    if (dr)
+        for (int j = threadIdx.x; j < rank; j += blockDim.x) ss += dr[j] * dr[j];
     const float inv = rsqrtf(block_sum(ss, scratch) / (float)rank + eps);      // also orders the writes of trig
 
     T* dst = nullptr;
-    if (slot_mapping) {
+    if (slot_mapping && dr) {
         const long long slot = slot_mapping[t];
         if (slot >= num_slots) {
             if (threadIdx.x == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);

@@ -29,17 +29,28 @@ __device__ __forceinline__ float expert_activation(float g, float u, float limit
     return g / (1.f + expf(-g)) * u;
 }
 
+// What an expert without a gate does with its one product.
+__device__ __forceinline__ float squared_relu(float z) { return z > 0.f ? z * z : 0.f; }
+
 // One warp per token.  ties go to the lower expert index.  ``over_chosen`` 0: the weights are the chosen experts' shares of
 // the softmax over all logits; 1: the ``top`` largest logits are chosen and the weights are the softmax over those alone.
+// ``correction`` (one number per expert, may be null; over_chosen 0 only): added to the shares for the choice, not for the
+// weights.  ``groups`` > 1: the experts form that many equal groups of neighbours; a group's score is its largest (corrected)
+// share, and only experts of the ``keep`` best groups can be chosen (ties to the lower group).
 __global__ void route_top_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weights,
-                                 int T, int experts, int top, float scale, int over_chosen) {
+                                 int T, int experts, int top, float scale, int over_chosen, const float* __restrict__ correction,
+                                 int groups, int keep) {
     griddep_wait();
     griddep_launch_dependents();
-    extern __shared__ float rows[];               // [warps][experts]
+    extern __shared__ float rows[];               // a warp: what it ranks by [experts], the shares [experts], groups [2 groups]
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + w;
     if (t >= T) return;
-    float* s = rows + (size_t)w * experts;
+    float* s = rows + (size_t)w * (2 * experts + 2 * groups);
+    float* share_of = s + experts;
+    float* group_score = share_of + experts;      // [groups], then 1 for a kept group [groups]
+    float* group_kept = group_score + groups;
+    const bool corrected = !over_chosen && (correction != nullptr || groups > 1);
     const float* z = logits + (size_t)t * experts;
     float m = -CUDART_INF_F;
     for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
@@ -52,6 +63,42 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
     }
     sum = warp_sum(sum);
     __syncwarp();
+    if (corrected) {
+        // ranked by share + correction; the share itself is kept for the weight
+        for (int e = lane; e < experts; e += 32) {
+            const float share = s[e] / sum;
+            share_of[e] = share;
+            s[e] = share + (correction ? correction[e] : 0.f);
+        }
+        __syncwarp();
+        if (groups > 1) {
+            const int size = experts / groups;
+            for (int g = lane; g < groups; g += 32) {
+                float best = -CUDART_INF_F;
+                for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, s[e]);
+                group_score[g] = best;
+                group_kept[g] = 0.f;
+            }
+            __syncwarp();
+            for (int round = 0; round < keep; ++round) {
+                float best = -CUDART_INF_F;
+                int at = groups;
+                for (int g = lane; g < groups; g += 32)
+                    if (group_kept[g] == 0.f && (at == groups || group_score[g] > best)) { best = group_score[g]; at = g; }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (oa < groups && (at >= groups || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+                }
+                if (at < groups && lane == 0) group_kept[at] = 1.f;
+                __syncwarp();
+            }
+            for (int e = lane; e < experts; e += 32)
+                if (group_kept[e / size] == 0.f) s[e] = -CUDART_INF_F;
+            __syncwarp();
+        }
+    }
     float chosen_sum = 0.f;
     for (int c = 0; c < top; ++c) {
         float best = -CUDART_INF_F;
@@ -68,7 +115,8 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
         if (lane == 0) {
             const float share = over_chosen ? expf(best - m) : best;      // m is the largest logit, the first one chosen
             chosen[(size_t)t * top + c] = at;
-            weights[(size_t)t * top + c] = over_chosen ? share : share / sum * scale;
+            if (corrected) weights[(size_t)t * top + c] = share_of[at] * scale;
+            else weights[(size_t)t * top + c] = over_chosen ? share : share / sum * scale;
             chosen_sum += share;
             s[at] = -CUDART_INF_F;
         }
@@ -81,20 +129,24 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
 }
 
 extern "C" int fe_route_top(const float* logits, int* chosen, float* weights, int T, int experts, int top, float scale,
-                            int over_chosen, cudaStream_t stream) {
+                            int over_chosen, const float* correction, int groups, int keep, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && top >= 1 && top <= experts,
                "route_top: bad sizes (experts %d, top %d; at most %d experts)", experts, top, ROUTE_MAX_EXPERTS);
+    FE_REQUIRE(groups >= 1 && experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups),
+               "route_top: %d groups of which %d are kept do not fit %d experts with %d chosen", groups, keep, experts, top);
+    FE_REQUIRE(!over_chosen || (correction == nullptr && groups == 1), "route_top: a correction and groups rank shares of the softmax over all experts");
     if (T == 0) return 0;
     const int warps = 4;
-    fe::launch(route_top_kernel, (T + warps - 1) / warps, warps * 32, (size_t)warps * experts * sizeof(float), stream, logits,
-               chosen, weights, T, experts, top, scale, over_chosen);
+    fe::launch(route_top_kernel, (T + warps - 1) / warps, warps * 32, (size_t)warps * (2 * experts + 2 * groups) * sizeof(float), stream,
+               logits, chosen, weights, T, experts, top, scale, over_chosen, correction, groups, keep);
     return fe_check_launch("route_top");
 }
 
 // One block.  pairs = T * top.  Outputs: offsets[experts + 1] (rows of expert e are offsets[e] .. offsets[e+1]),
 // row_of_pair[pairs], pair_of_row[pairs], and the tiles of ``tile_rows`` rows: tile_expert[], tile_row0[], with
-// tiles[0] = how many there are.
-__global__ void route_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int tile_rows, int* __restrict__ offsets,
+// tiles[0] = how many there are.  A choice in [experts, experts + identity) stands for an expert that returns its input: it
+// gets no row (row_of_pair = -2) and the combination adds the token's own row for it.
+__global__ void route_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int identity, int tile_rows, int* __restrict__ offsets,
                                   int* __restrict__ row_of_pair, int* __restrict__ pair_of_row, int* __restrict__ tiles,
                                   int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ status) {
     griddep_wait();
@@ -106,7 +158,7 @@ __global__ void route_plan_kernel(const int* __restrict__ chosen, int pairs, int
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = chosen[p];
         if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
-        else if (status) atomicOr(status, FE_STATUS_BAD_SLOT);
+        else if ((e < 0 || e >= experts + identity) && status) atomicOr(status, FE_STATUS_BAD_SLOT);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -127,7 +179,7 @@ __global__ void route_plan_kernel(const int* __restrict__ chosen, int pairs, int
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = chosen[p];
-        if (e < 0 || e >= experts) { row_of_pair[p] = -1; continue; }
+        if (e < 0 || e >= experts) { row_of_pair[p] = (e >= experts && e < experts + identity) ? -2 : -1; continue; }
         const int row = atomicAdd(&cursor[e], 1);
         row_of_pair[p] = row;
         pair_of_row[row] = p;
@@ -135,18 +187,20 @@ __global__ void route_plan_kernel(const int* __restrict__ chosen, int pairs, int
 }
 
 // The two grouped products.  Tile 64 rows x 64 columns, 16 of K a stage, 256 threads with 4 x 4 outputs each; float
-// accumulation in ascending k.  GATED: columns n and n + F of the expert's matrix are taken together and
-// silu(gate) * up is written (compute type); otherwise the plain product is written in float.
+// accumulation in ascending k.  MODE 1 (GATED): columns n and n + F of the expert's matrix are taken together and
+// silu(gate) * up is written (compute type); MODE 2: an expert without a gate, relu(product)^2 is written (compute type);
+// MODE 0: the plain product is written in float.
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
-template <typename T, bool GATED>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
                       void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
                       const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     griddep_wait();
     griddep_launch_dependents();
+    constexpr bool GATED = MODE == 1;
     if ((int)blockIdx.y >= tiles[0]) return;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
@@ -213,6 +267,8 @@ routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_r
             if (GATED) {
                 const float g = acc[i][j];
                 reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, acu[i][j], limit));
+            } else if (MODE == 2) {
+                reinterpret_cast<T*>(out)[at] = from_float<T>(squared_relu(acc[i][j]));
             } else {
                 reinterpret_cast<float*>(out)[at] = acc[i][j];
             }
@@ -227,13 +283,14 @@ routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_r
 // GATED), multiply with all rows, and add up over the warp.
 constexpr int FEW_ROWS = 8, FEW_ROWS_SMALL = 4, FEW_WARPS = 8, FEW_COLS = 4;
 
-template <typename T, bool GATED, int ROWS>
+template <typename T, int MODE, int ROWS>
 __global__ void __launch_bounds__(FEW_WARPS * 32)
 routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K, float limit) {
     griddep_wait();
     griddep_launch_dependents();
+    constexpr bool GATED = MODE == 1;
     if ((int)blockIdx.y >= tiles[0]) return;
     extern __shared__ __align__(16) unsigned char few_smem[];
     T* rows_s = reinterpret_cast<T*>(few_smem);                 // [ROWS][K]
@@ -313,6 +370,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
                 if (lane == 0 && nbase + c < N) {
                     const size_t at = (size_t)(row0 + r) * N + nbase + c;
                     if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, u, limit));
+                    else if (MODE == 2) reinterpret_cast<T*>(out)[at] = from_float<T>(squared_relu(g));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -346,6 +404,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
             if (lane == 0 && r < rows) {
                 const size_t at = (size_t)(row0 + r) * N + n;
                 if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(expert_activation(g, u, limit));
+                else if (MODE == 2) reinterpret_cast<T*>(out)[at] = from_float<T>(squared_relu(g));
                 else reinterpret_cast<float*>(out)[at] = g;
             }
         }
@@ -356,7 +415,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
 // 64 columns (and the 64 paired "up" columns when GATED), 32 of K a stage, 4 warps with 32 x 32 outputs each.
 constexpr int TBM = 64, TBN = 64, TBK = 32, TLD = TBK + 8;
 
-template <bool GATED>
+template <int MODE, bool GATED = (MODE == 1)>
 __global__ void __launch_bounds__(128)
 routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
@@ -452,6 +511,7 @@ routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pa
                     const size_t at = (size_t)(row0 + r) * N + gn;
                     const float g = stage[warp][0][rr][cc];
                     if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(expert_activation(g, stage[warp][GATED ? 1 : 0][rr][cc], limit));
+                    else if (MODE == 2) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(squared_relu(g));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -473,7 +533,7 @@ __device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool GATED>
+template <int MODE, bool GATED = (MODE == 1)>
 __global__ void __launch_bounds__(256)
 routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
                            void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
@@ -574,6 +634,7 @@ routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ p
                     const size_t at = (size_t)(row0 + r) * N + gn;
                     const float g = mine[rr * 20 + cc];
                     if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(expert_activation(g, mine[16 * 20 + rr * 20 + cc], limit));
+                    else if (MODE == 2) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(squared_relu(g));
                     else reinterpret_cast<float*>(out)[at] = g;
                 }
             }
@@ -581,11 +642,12 @@ routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ p
         }
 }
 
-// out[t] = sum_c weights[t][c] * y[row_of_pair[t top + c]] (+ shared[t])
+// out[t] = sum_c weights[t][c] * y[row_of_pair[t top + c]] (+ shared[t]); a choice of an expert that returns its input
+// (row -2) adds weights[t][c] * h[t]
 template <typename T>
 __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                       const float* __restrict__ weights, const T* __restrict__ shared, T* __restrict__ out,
-                                      int top, int D) {
+                                      int top, int D, const T* __restrict__ h) {
     griddep_wait();
     griddep_launch_dependents();
     const int t = blockIdx.x;
@@ -594,6 +656,7 @@ __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __
         for (int c = 0; c < top; ++c) {
             const int row = row_of_pair[(size_t)t * top + c];
             if (row >= 0) total = fmaf(weights[(size_t)t * top + c], y[(size_t)row * D + j], total);
+            else if (row == -2 && h) total = fmaf(weights[(size_t)t * top + c], to_float(h[(size_t)t * D + j]), total);
         }
         if (shared) total += to_float(shared[(size_t)t * D + j]);
         out[(size_t)t * D + j] = from_float<T>(total);
@@ -610,10 +673,13 @@ extern "C" long long fe_routed_experts_workspace(int T, int top, int experts, in
 }
 
 // h [T, D]; chosen, weights [T, top]; gate_up [experts, 2F, D]; down [experts, D, F]; shared [T, D] or null; out [T, D].
-// limit: 0 for silu(gate) * up, else the clamped activation (see expert_activation).
+// limit: 0 for silu(gate) * up, else the clamped activation (see expert_activation).  single 1: the experts have no gate,
+// gate_up is [experts, F, D] and an expert is down(relu(up h)^2).  identity: choices in [experts, experts + identity) stand
+// for experts that return their input.
 extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* weights, const void* gate_up, const void* down,
                                  const void* shared, void* out, void* workspace, long long workspace_bytes, int T, int top,
-                                 int experts, int D, int F, int dtype, float limit, int* status, cudaStream_t stream) {
+                                 int experts, int D, int F, int dtype, float limit, int* status, int single, int identity,
+                                 cudaStream_t stream) {
     FE_REQUIRE(limit >= 0.f, "routed_experts: the activation's limit is 0 (plain silu) or positive");
     FE_REQUIRE(T >= 0 && top >= 1 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && D > 0 && F > 0, "routed_experts: bad sizes");
     FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "routed_experts: unknown dtype %d", dtype);
@@ -640,8 +706,9 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     const bool few = pairs <= 64 && few_smem1 <= 160 * 1024 && few_smem2 <= 160 * 1024;
     // tensor cores with 128-row tiles and pipelined copies when rows start on 16-byte boundaries in both products
     const bool piped = !few && dtype == FE_BF16 && D % 8 == 0 && F % 8 == 0;
-    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? few_rows : (piped ? PBM : BM), offsets, row_of_pair,
-               pair_of_row, tiles, tile_expert, tile_row0, status);
+    FE_REQUIRE(identity >= 0 && (single == 0 || single == 1), "routed_experts: bad options");
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, identity, few ? few_rows : (piped ? PBM : BM), offsets,
+               row_of_pair, pair_of_row, tiles, tile_expert, tile_row0, status);
     const int* c_pairs = pair_of_row;
     const int* c_none = nullptr;
     const int *c_offsets = offsets, *c_tiles = tiles, *c_expert = tile_expert, *c_row0 = tile_row0;
@@ -658,12 +725,19 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     do {                                                                                                                                \
         cudaError_t err = cudaSuccess;                                                                                                  \
         if (few_smem1 > 48 * 1024)                                                                                                      \
-            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, true, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1); \
+            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, 1, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1); \
         if (err == cudaSuccess && few_smem2 > 48 * 1024)                                                                                \
-            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, false, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2); \
+            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, 0, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2); \
+        if (err == cudaSuccess && few_smem1 > 48 * 1024)                                                                                \
+            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, 2, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1); \
         FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));                                                  \
-        FE_ROUTED_PRODUCTS((routed_product_few_kernel<TYPE, true, ROWS>), (routed_product_few_kernel<TYPE, false, ROWS>), TYPE, g1, g2, \
-                           FEW_WARPS * 32, few_smem1, few_smem2);                                                                       \
+        if (single) {                                                                                                                   \
+            FE_ROUTED_PRODUCTS((routed_product_few_kernel<TYPE, 2, ROWS>), (routed_product_few_kernel<TYPE, 0, ROWS>), TYPE, g1, g2,    \
+                               FEW_WARPS * 32, few_smem1, few_smem2);                                                                   \
+        } else {                                                                                                                        \
+            FE_ROUTED_PRODUCTS((routed_product_few_kernel<TYPE, 1, ROWS>), (routed_product_few_kernel<TYPE, 0, ROWS>), TYPE, g1, g2,    \
+                               FEW_WARPS * 32, few_smem1, few_smem2);                                                                   \
+        }                                                                                                                               \
     } while (0)
         if (dtype == FE_F32) {
             if (few_rows == FEW_ROWS_SMALL) FE_ROUTED_FEW(float, FEW_ROWS_SMALL);
@@ -676,15 +750,19 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     } else {
         const dim3 grid1((F + BN - 1) / BN, max_tiles), grid2((D + BN - 1) / BN, max_tiles);
         if (dtype == FE_F32) {
-            FE_ROUTED_PRODUCTS((routed_product_kernel<float, true>), (routed_product_kernel<float, false>), float, grid1, grid2, 256, 0, 0);
+            if (single) { FE_ROUTED_PRODUCTS((routed_product_kernel<float, 2>), (routed_product_kernel<float, 0>), float, grid1, grid2, 256, 0, 0); }
+            else { FE_ROUTED_PRODUCTS((routed_product_kernel<float, 1>), (routed_product_kernel<float, 0>), float, grid1, grid2, 256, 0, 0); }
         } else if (piped) {
-            cudaError_t err = cudaFuncSetAttribute(routed_product_pipe_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
-            if (err == cudaSuccess) err = cudaFuncSetAttribute(routed_product_pipe_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
+            cudaError_t err = cudaFuncSetAttribute(routed_product_pipe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
+            if (err == cudaSuccess) err = cudaFuncSetAttribute(routed_product_pipe_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
+            if (err == cudaSuccess) err = cudaFuncSetAttribute(routed_product_pipe_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
             FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
             const dim3 p1((F + PBN - 1) / PBN, max_tiles), p2((D + PBN - 1) / PBN, max_tiles);
-            FE_ROUTED_PRODUCTS((routed_product_pipe_kernel<true>), (routed_product_pipe_kernel<false>), bf16, p1, p2, 256, PIPE_SMEM_BYTES, PIPE_SMEM_BYTES);
+            if (single) { FE_ROUTED_PRODUCTS((routed_product_pipe_kernel<2>), (routed_product_pipe_kernel<0>), bf16, p1, p2, 256, PIPE_SMEM_BYTES, PIPE_SMEM_BYTES); }
+            else { FE_ROUTED_PRODUCTS((routed_product_pipe_kernel<1>), (routed_product_pipe_kernel<0>), bf16, p1, p2, 256, PIPE_SMEM_BYTES, PIPE_SMEM_BYTES); }
         } else {
-            FE_ROUTED_PRODUCTS((routed_product_mma_kernel<true>), (routed_product_mma_kernel<false>), bf16, grid1, grid2, 128, 0, 0);
+            if (single) { FE_ROUTED_PRODUCTS((routed_product_mma_kernel<2>), (routed_product_mma_kernel<0>), bf16, grid1, grid2, 128, 0, 0); }
+            else { FE_ROUTED_PRODUCTS((routed_product_mma_kernel<1>), (routed_product_mma_kernel<0>), bf16, grid1, grid2, 128, 0, 0); }
         }
     }
 #undef FE_ROUTED_PRODUCTS
@@ -692,10 +770,10 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     const dim3 combine(T, stretches < 65535 ? stretches : 65535);
     if (dtype == FE_F32)
         fe::launch(routed_combine_kernel<float>, combine, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
-                   (const float*)shared, (float*)out, top, D);
+                   (const float*)shared, (float*)out, top, D, identity ? (const float*)h : (const float*)nullptr);
     else
         fe::launch(routed_combine_kernel<bf16>, combine, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
-                   (const bf16*)shared, (bf16*)out, top, D);
+                   (const bf16*)shared, (bf16*)out, top, D, identity ? (const bf16*)h : (const bf16*)nullptr);
     return fe_check_launch("routed_experts");
 }
 
@@ -703,9 +781,9 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
 // The pieces on their own, for a caller that takes the two products elsewhere (the grouped tcgen05 GEMM of the
 // bfloat16 library): the plan, the rows of h gathered into sorted order, and the combination.
 extern "C" int fe_routed_plan(const int* chosen, int pairs, int experts, int tile_rows, int* offsets, int* row_of_pair,
-                              int* pair_of_row, int* tiles, int* tile_expert, int* tile_row0, int* status, cudaStream_t stream) {
-    FE_REQUIRE(pairs >= 1 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && tile_rows >= 1, "routed_plan: bad sizes");
-    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, pairs, experts, tile_rows, offsets, row_of_pair, pair_of_row, tiles,
+                              int* pair_of_row, int* tiles, int* tile_expert, int* tile_row0, int* status, int identity, cudaStream_t stream) {
+    FE_REQUIRE(pairs >= 1 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && tile_rows >= 1 && identity >= 0, "routed_plan: bad sizes");
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, pairs, experts, identity, tile_rows, offsets, row_of_pair, pair_of_row, tiles,
                tile_expert, tile_row0, status);
     return fe_check_launch("routed_plan");
 }
@@ -713,33 +791,38 @@ extern "C" int fe_routed_plan(const int* chosen, int pairs, int experts, int til
 namespace {
 // sorted[row] = h[pair_of_row[row] / top]: 16 bytes a thread and step (bytes_per_row is a multiple of 16)
 __global__ void routed_gather_kernel(const uint4* __restrict__ h, const int* __restrict__ pair_of_row, int top,
-                                     uint4* __restrict__ sorted, int pieces) {
+                                     uint4* __restrict__ sorted, int pieces, const int* __restrict__ sorted_rows) {
     griddep_wait();
     griddep_launch_dependents();
     const int row = blockIdx.x;
+    if (sorted_rows && row >= *sorted_rows) return;          // pairs that have no row (experts that return their input)
     const int src = pair_of_row[row] / top;
     for (int p = threadIdx.x; p < pieces; p += blockDim.x) sorted[(size_t)row * pieces + p] = h[(size_t)src * pieces + p];
 }
 }  // namespace
 
+// sorted_rows (may be null): where the number of sorted rows lies on the device, when it can be fewer than ``pairs``
 extern "C" int fe_routed_gather(const void* h, const int* pair_of_row, int top, void* sorted, int pairs, long long bytes_per_row,
+                                const int* sorted_rows,
                                 cudaStream_t stream) {
     FE_REQUIRE(pairs >= 1 && top >= 1 && bytes_per_row > 0 && bytes_per_row % 16 == 0 && ((((size_t)h) | ((size_t)sorted)) & 15) == 0,
                "routed_gather: rows must be multiples of 16 bytes on 16-byte boundaries");
-    fe::launch(routed_gather_kernel, pairs, 128, 0, stream, (const uint4*)h, pair_of_row, top, (uint4*)sorted, (int)(bytes_per_row / 16));
+    fe::launch(routed_gather_kernel, pairs, 128, 0, stream, (const uint4*)h, pair_of_row, top, (uint4*)sorted, (int)(bytes_per_row / 16), sorted_rows);
     return fe_check_launch("routed_gather");
 }
 
 extern "C" int fe_routed_combine(const float* y, const int* row_of_pair, const float* weights, const void* shared, void* out, int T,
-                                 int top, int D, int dtype, cudaStream_t stream) {
+                                 int top, int D, int dtype, const void* identity_rows, cudaStream_t stream) {
     FE_REQUIRE(T >= 1 && top >= 1 && D >= 1, "routed_combine: bad sizes");
     const int threads = D >= 1024 ? 256 : 128;
     const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;
     const dim3 grid(T, stretches < 65535 ? stretches : 65535);
     if (dtype == FE_F32)
-        fe::launch(routed_combine_kernel<float>, grid, threads, 0, stream, y, row_of_pair, weights, (const float*)shared, (float*)out, top, D);
+        fe::launch(routed_combine_kernel<float>, grid, threads, 0, stream, y, row_of_pair, weights, (const float*)shared, (float*)out, top, D,
+                   (const float*)identity_rows);
     else if (dtype == FE_BF16)
-        fe::launch(routed_combine_kernel<bf16>, grid, threads, 0, stream, y, row_of_pair, weights, (const bf16*)shared, (bf16*)out, top, D);
+        fe::launch(routed_combine_kernel<bf16>, grid, threads, 0, stream, y, row_of_pair, weights, (const bf16*)shared, (bf16*)out, top, D,
+                   (const bf16*)identity_rows);
     else
         FE_REQUIRE(false, "routed_combine: unknown dtype %d", dtype);
     return fe_check_launch("routed_combine");

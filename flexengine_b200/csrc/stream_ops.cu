@@ -186,6 +186,7 @@ extern "C" int fe_depth_average(float* history, float* x, const void* a, const v
 // ---------------------------------------------------------------------------------------------
 // Elementwise activations.  kind 0: tanh.  kind 1: xIELU with the two numbers params = (p, q) on the device:
 //   z > 0: softplus(p) z^2 + z/2;    z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2.
+// kind 2: the square of relu(z).
 __device__ __forceinline__ float softplusf(float v) { return log1pf(expf(v)); }
 
 template <typename T>
@@ -206,6 +207,7 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 if (kind == 0) z[e] = tanhf(z[e]);
+                else if (kind == 2) z[e] = z[e] > 0.f ? z[e] * z[e] : 0.f;
                 else z[e] = z[e] > 0.f ? fmaf(up * z[e], z[e], 0.5f * z[e]) : fmaf(down, expm1f(z[e]) - z[e], 0.5f * z[e]);
             }
             store8<T>(out + i, z);
@@ -216,6 +218,7 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
         const float z = to_float(x[i]);
         float y;
         if (kind == 0) y = tanhf(z);
+        else if (kind == 2) y = z > 0.f ? z * z : 0.f;
         else y = z > 0.f ? fmaf(up * z, z, 0.5f * z) : fmaf(down, expm1f(z) - z, 0.5f * z);
         out[i] = from_float<T>(y);
     }
@@ -223,7 +226,7 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
 
 extern "C" int fe_activation(const void* x, void* out, long long n, int kind, const float* params, int dtype,
                              cudaStream_t stream) {
-    FE_REQUIRE(n >= 0 && (kind == 0 || (kind == 1 && params != nullptr)), "activation: bad arguments (kind %d)", kind);
+    FE_REQUIRE(n >= 0 && (kind == 0 || kind == 2 || (kind == 1 && params != nullptr)), "activation: bad arguments (kind %d)", kind);
     if (n == 0) return 0;
     const int threads = 256;
     const long long want = (n / 8 + threads) / threads;

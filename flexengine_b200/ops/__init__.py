@@ -303,6 +303,7 @@ def linear(x, w, bias=None, out_float32=False, follow=None, upcoming=None):
 SKINNY_MAX_ROWS = 8          # beyond this the library product is as fast or faster
 SKINNY_QKV_MAX_ROWS = 8      # the fused projection + bias + rotation + cache write takes one 8-row tile of tokens
 EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 5      # 5: the gated epilogue with the tanh form of GELU
+EPI_RELU2 = 6                                               # relu(product)^2, no gate
 GATED_EPILOGUES = {"silu": EPI_SWIGLU, "gelu_tanh": EPI_GEGLU}
 
 
@@ -492,14 +493,18 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     return qkv
 
 
+ATTENTION_SINK, ATTENTION_SIGMOID = 1, 2       # bits of the attention kernels' mode
+
+
 def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, token_request, T, nq, nkv, d,
-                         page_size, scale, window, sink=False):
+                         page_size, scale, window, sink=False, sigmoid=False, head_bias=None):
     out = torch.empty((T, nq * d), dtype=k_cache.dtype, device=k_cache.device)
+    mode = (ATTENTION_SINK if sink else 0) | (ATTENTION_SIGMOID if sigmoid else 0)
     _run(_core(), "fe_paged_attention_simt", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _ptr(token_request), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size),
-         _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(_code(k_cache.dtype)),
-         _ptr(status_word(k_cache.device)), _stream())
+         _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window), _c_int(mode), _c_int(_code(k_cache.dtype)),
+         _ptr(status_word(k_cache.device)), _ptr(head_bias), _stream())
     return out
 
 
@@ -694,11 +699,14 @@ def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_st
     return out
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False,
+                    weights="softmax", head_bias=None):
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
     ``window``: what a query sees of the earlier keys: 0 all of them, w > 0 the last w, -c < 0 those of its own chunk of
     c positions (counted from position 0).  ``sink``: 1 is added to the softmax's denominator.
+    ``weights`` "sigmoid": no softmax; a visible key weighs sigmoid(score + head_bias[head]) (``head_bias`` float32 [nq] or
+    None), not normalised over the keys.
     float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
     kernel when every request brings one token, else a prefill kernel (tcgen05 for portions of
     head size 64 or 128, mma.sync otherwise)."""
@@ -706,9 +714,16 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     T = qkv.shape[0]
     if qkv.dtype != k_cache.dtype:
         raise TypeError("queries and cache differ in dtype")
-    if qkv.dtype == torch.float32 or d > 256:          # the tensor-core kernels take head sizes up to 256
+    if weights not in ("softmax", "sigmoid") or (weights == "sigmoid" and sink):
+        raise ValueError("paged_attention: weights are 'softmax' (with or without a sink) or 'sigmoid'")
+    sigmoid = weights == "sigmoid"
+    if head_bias is not None:
+        _need_cuda(head_bias)
+        if not sigmoid or head_bias.dtype != torch.float32 or head_bias.numel() != nq:
+            raise ValueError("paged_attention: a head bias goes with sigmoid weights and is float32 [heads]")
+    if qkv.dtype == torch.float32 or d > 256 or sigmoid:          # the tensor-core kernels take head sizes up to 256
         return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
-                                    ctx.token_request, T, nq, nkv, d, page_size, scale, window, sink)
+                                    ctx.token_request, T, nq, nkv, d, page_size, scale, window, sink, sigmoid, head_bias)
     requests = ctx.cu_q.numel() - 1
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         # a window or a chunk bounds the keys a token walks (plus the tile of 32 that its first key lies in)
@@ -835,6 +850,63 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
     return queries
 
 
+ROTATION_PAIRS = {"halves": 0, "interleaved": 1}
+
+
+def qkv_norm_rope_cache(projected, q_weight, k_weight, eps, positions, inv_freq, rot_dims, pairs, value_inv_freq, slot_mapping,
+                        k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+    """What attention does between its projection and its scores, second form (csrc/hyper_ops.cu).  ``projected``
+    [T, >= channels] holds q | k | v.  One RMS norm over the WHOLE query projection with ``q_weight`` (float32
+    [heads dim]) and one over the whole key projection with ``k_weight`` ([kv_heads dim]; both None: no norm), then the
+    first ``rot_dims`` entries of every query and key head turned by position * inv_freq, ``pairs`` "interleaved"
+    (2i with 2i + 1) or "halves" (i with i + rot_dims/2); the values turned over all ``vdim`` entries by position *
+    value_inv_freq (None: as they are); keys and values into their cache slots (slot_mapping None: no write) and the
+    queries returned [T, heads head], all padded with zeros to ``head``."""
+    _need_cuda(projected, q_weight, k_weight, positions, inv_freq, value_inv_freq, slot_mapping, k_cache, v_cache)
+    T = projected.shape[0]
+    channels = (heads + kv_heads) * dim + kv_heads * vdim
+    if projected.dim() != 2 or projected.shape[1] < channels or projected.stride(1) != 1:
+        raise ValueError("qkv_norm_rope_cache: projected is [T, >= channels] with unit column stride")
+    if (q_weight is None) != (k_weight is None) or (q_weight is not None and (
+            q_weight.dtype != torch.float32 or k_weight.dtype != torch.float32 or q_weight.numel() != heads * dim
+            or k_weight.numel() != kv_heads * dim)):
+        raise ValueError("qkv_norm_rope_cache: the norm weights are float32 [heads dim] and [kv_heads dim]")
+    if k_cache.dtype != projected.dtype or tuple(k_cache.shape[1:]) != (kv_heads, page_size, head) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or v_cache.shape != k_cache.shape:
+        raise ValueError("qkv_norm_rope_cache: caches are contiguous [pages, kv_heads, page_size, head] in the compute dtype")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise ValueError("inv_freq must be float32 [rot_dims / 2]")
+    if value_inv_freq is not None and (value_inv_freq.dtype != torch.float32 or value_inv_freq.numel() != vdim // 2 or vdim % 2):
+        raise ValueError("value_inv_freq must be float32 [vdim / 2]")
+    if pairs not in ROTATION_PAIRS:
+        raise ValueError(f"unknown layout of rotation pairs {pairs!r}; known: {sorted(ROTATION_PAIRS)}")
+    queries = torch.empty((T, heads * head), dtype=projected.dtype, device=projected.device)
+    _run(_core(), "fe_qkv_norm_rope_cache", _ptr(projected), _c_ll(projected.stride(0)), _ptr(q_weight), _ptr(k_weight), _c_float(eps),
+         _ptr(positions), _ptr(inv_freq), _c_int(rot_dims if inv_freq is not None else 0), _c_int(ROTATION_PAIRS[pairs]),
+         _ptr(value_inv_freq), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _ptr(queries), _c_int(T), _c_int(heads), _c_int(kv_heads),
+         _c_int(dim), _c_int(vdim), _c_int(head), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _c_int(_code(projected.dtype)),
+         _ptr(status_word(projected.device)), _stream())
+    return queries
+
+
+def unrotate_heads(mixed, positions, inv_freq, heads, head, vdim, pairs, scale=1.0, out=None):
+    """[T, heads vdim]: the first ``vdim`` entries of every head of ``mixed`` [T, heads head] turned BACK by the token's
+    position (pair m by -position * inv_freq[m]; ``pairs`` as in ``qkv_norm_rope_cache``), times ``scale``.  ``out``: where
+    the rows go (a view with any row stride)."""
+    _need_cuda(mixed, positions, inv_freq, out)
+    T = mixed.shape[0]
+    if tuple(mixed.shape) != (T, heads * head) or not mixed.is_contiguous() or inv_freq.dtype != torch.float32 \
+            or inv_freq.numel() != vdim // 2 or vdim % 2 or pairs not in ROTATION_PAIRS:
+        raise ValueError("unrotate_heads: mixed is contiguous [T, heads head]; inv_freq float32 [vdim / 2]")
+    if out is None:
+        out = torch.empty((T, heads * vdim), dtype=mixed.dtype, device=mixed.device)
+    elif tuple(out.shape) != (T, heads * vdim) or out.dtype != mixed.dtype or out.stride(1) != 1:
+        raise ValueError("unrotate_heads: out is [T, heads vdim] in the compute dtype with unit column stride")
+    _run(_core(), "fe_unrotate_heads", _ptr(mixed), _ptr(positions), _ptr(inv_freq), _ptr(out), _c_ll(out.stride(0)), _c_int(T),
+         _c_int(heads), _c_int(head), _c_int(vdim), _c_int(ROTATION_PAIRS[pairs]), _c_float(scale), _c_int(_code(mixed.dtype)), _stream())
+    return out
+
+
 def head_gate(mixed, projected, offset, heads, head, vdim, per_element=False, scale=1.0, out=None):
     """[T, heads vdim]: out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h]) * scale; ``mixed``
     [T, heads head].  With ``per_element`` the gate of entry j of head h is projected[t, offset + h vdim + j].  ``out``: where
@@ -933,12 +1005,12 @@ def depth_average(history, x, mixed, fed, alpha, depth):
          _c_ll(x.numel()), _c_int(_code(mixed.dtype)), _stream())
 
 
-ACTIVATIONS = {"tanh": 0, "xielu": 1}
+ACTIVATIONS = {"tanh": 0, "xielu": 1, "relu2": 2}
 
 
 def activation(x, kind, params=None):
-    """Elementwise, float arithmetic, the input's dtype out: "tanh", or "xielu" with params = (p, q) on the device:
-    z > 0: softplus(p) z^2 + z/2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+    """Elementwise, float arithmetic, the input's dtype out: "tanh", "relu2" (the square of relu), or "xielu" with
+    params = (p, q) on the device: z > 0: softplus(p) z^2 + z/2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
     _need_cuda(x, params)
     if kind not in ACTIVATIONS:
         raise ValueError(f"unknown activation {kind!r}; known: {sorted(ACTIVATIONS)}")
@@ -948,6 +1020,11 @@ def activation(x, kind, params=None):
     _run(_core(), "fe_activation", _ptr(x), _ptr(out), _c_ll(x.numel()), _c_int(ACTIVATIONS[kind]), _ptr(params),
          _c_int(_code(x.dtype)), _stream())
     return out
+
+
+def linear_activated(x, w, kind):
+    """act(x w^T) for an activation without parameters ("relu2", "tanh"): the product, then the activation kernel."""
+    return activation(linear(x, w), kind)
 
 
 # ---- the linear-recurrent mixer ---------------------------------------------------------------------------------
@@ -1108,14 +1185,18 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
     ``rot_dims`` entries, float32 angles), this step's rows [latent | key part | 0] into their cache slots
     (``rows`` [pages, 1, page_size, row]; slot_mapping None: no write), and the queries [T, heads row] =
     [q_latent | rotated query part | 0] per head.  q [T, heads (dim + rot_dim)], q_latent [heads, T, rank] in the
-    compute dtype; down [T, rank + rot_dim] float32."""
+    compute dtype; down [T, rank + rot_dim] float32, or None for a layer that reads the rows another layer cached: only
+    the queries are made then."""
     _need_cuda(q, q_latent, down, norm_weight, positions, inv_freq, slot_mapping, rows)
     T = q.shape[0]
-    if down.dtype != torch.float32 or norm_weight.dtype != torch.float32 or inv_freq.dtype != torch.float32 \
-            or tuple(q.shape) != (T, heads * (dim + rot_dim)) or tuple(q_latent.shape) != (heads, T, rank) \
-            or tuple(down.shape) != (T, rank + rot_dim) or inv_freq.numel() != rot_dims // 2 \
-            or not (q.is_contiguous() and q_latent.is_contiguous() and down.is_contiguous()):
+    if inv_freq.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)) or tuple(q_latent.shape) != (heads, T, rank) \
+            or inv_freq.numel() != rot_dims // 2 or not (q.is_contiguous() and q_latent.is_contiguous()):
         raise ValueError("latent_prepare: shapes or dtypes do not fit")
+    if down is not None and (down.dtype != torch.float32 or norm_weight is None or norm_weight.dtype != torch.float32
+                             or tuple(down.shape) != (T, rank + rot_dim) or not down.is_contiguous()):
+        raise ValueError("latent_prepare: the latent's projection is contiguous float32 [T, rank + rot_dim], its norm weight float32")
+    if down is None:
+        slot_mapping = None
     if rows.dtype != q.dtype or tuple(rows.shape[1:]) != (1, page_size, row) or not rows.is_contiguous():
         raise ValueError("latent_prepare: the cache is contiguous [pages, 1, page_size, row] in the compute dtype")
     queries = torch.empty((T, heads * row), dtype=q.dtype, device=q.device)
@@ -1127,23 +1208,31 @@ def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot
 
 
 # ---- a routed feed-forward ---------------------------------------------------------------------------------------
-def route_top(logits, top, scale, over_chosen=False):
+def route_top(logits, top, scale, over_chosen=False, correction=None, groups=(1, 1)):
     """(int32 [T, top], float32 [T, top]): per token the ``top`` largest softmax scores over all experts (float32, ties
     to the lower index) times ``scale``, and their experts.  ``over_chosen``: the ``top`` largest logits are chosen and the
-    weights are the softmax over those alone (times ``scale``)."""
-    _need_cuda(logits)
+    weights are the softmax over those alone (times ``scale``).  ``correction`` (float32, a number per expert) is added to
+    the scores for the choice only.  ``groups`` = (count, keep): the experts form ``count`` equal groups of neighbours, a
+    group's score is its largest (corrected) score, and only experts of the ``keep`` best groups can be chosen."""
+    _need_cuda(logits, correction)
     T, experts = logits.shape
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise TypeError("route_top: router logits are contiguous float32")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
+        raise ValueError("route_top: the correction is float32, a number per expert")
+    count, keep = (int(g) for g in groups)
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     _run(_core(), "fe_route_top", _ptr(logits), _ptr(chosen), _ptr(weights), _c_int(T), _c_int(experts), _c_int(top),
-         _c_float(scale), _c_int(1 if over_chosen else 0), _stream())
+         _c_float(scale), _c_int(1 if over_chosen else 0), _ptr(correction), _c_int(count), _c_int(keep), _stream())
     return chosen, weights
 
 
 ROUTED_TCGEN05_MIN_PAIRS = 1024     # fewer sorted rows than this: the mma.sync tiles of the core library
 ROUTED_TCGEN05_MIN_K = 1024          # narrower experts: level or behind (512 x 384: 0.090 against 0.052 ms at 2,048 rows)
+
+
+ROUTED_SINGLE = ("relu2",)            # activations of experts without a gate: one matrix up, one down
 
 
 def routed_tcgen05_ok(h, pairs, H, F) -> bool:
@@ -1153,13 +1242,13 @@ def routed_tcgen05_ok(h, pairs, H, F) -> bool:
             and min(H, F) >= ROUTED_TCGEN05_MIN_K and h.data_ptr() % 16 == 0)
 
 
-def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit=0.0):
+def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit=0.0, single=False, identity=0):
     """The routed feed-forward with its products on tcgen05 tensor cores: plan (counting sort, row tiles of 128 per
     expert), the rows of h gathered into sorted order, gate/up with the activation in the epilogue, down into float32,
     combination.  Everything stays on the device."""
     T, H = h.shape
     experts, F2, _ = gate_up.shape
-    F, top = F2 // 2, chosen.shape[1]
+    F, top = (F2 if single else F2 // 2), chosen.shape[1]
     pairs = T * top
     most_tiles = -(-pairs // 128) + experts
     dev = h.device
@@ -1170,48 +1259,52 @@ def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit=0.0
     status = status_word(dev)
     core, tensor = _core(), _bf16()
     _run(core, "fe_routed_plan", _ptr(chosen), _c_int(pairs), _c_int(experts), _c_int(128), _ptr(offsets), _ptr(row_of_pair),
-         _ptr(pair_of_row), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(status), _stream())
+         _ptr(pair_of_row), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(status), _c_int(identity), _stream())
     rows = torch.empty((pairs, H), dtype=torch.bfloat16, device=dev)
-    _run(core, "fe_routed_gather", _ptr(h), _ptr(pair_of_row), _c_int(top), _ptr(rows), _c_int(pairs), _c_ll(H * 2), _stream())
+    _run(core, "fe_routed_gather", _ptr(h), _ptr(pair_of_row), _c_int(top), _ptr(rows), _c_int(pairs), _c_ll(H * 2),
+         _ptr(offsets[experts:]), _stream())
     act = torch.empty((pairs, F), dtype=torch.bfloat16, device=dev)
-    _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(rows), _ptr(gate_up), _ptr(act), _c_int(pairs), _c_int(experts), _c_int(2 * F),
-         _c_int(H), _c_int(EPI_SWIGLU), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _c_float(limit), _ptr(status), _stream())
+    _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(rows), _ptr(gate_up), _ptr(act), _c_int(pairs), _c_int(experts), _c_int(F if single else 2 * F),
+         _c_int(H), _c_int(EPI_RELU2 if single else EPI_SWIGLU), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _c_float(limit), _ptr(status), _stream())
     y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
     _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(act), _ptr(down), _ptr(y), _c_int(pairs), _c_int(experts), _c_int(H), _c_int(F),
          _c_int(EPI_F32), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _c_float(0.0), _ptr(status), _stream())
     out = torch.empty((T, H), dtype=h.dtype, device=dev)
     _run(core, "fe_routed_combine", _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(shared), _ptr(out), _c_int(T), _c_int(top),
-         _c_int(H), _c_int(_code(h.dtype)), _stream())
+         _c_int(H), _c_int(_code(h.dtype)), _ptr(h) if identity else None, _stream())
     return out
 
 
-def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0):
+def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="silu", limit=0.0, identity=0):
     """out[t] = sum_c weights[t, c] * down_e( silu(gate_e h_t) * up_e h_t ) with e = chosen[t, c], plus ``shared`` [T, H] if
     given; gate_up [experts, 2F, H] ([gate; up] per expert), down [experts, H, F].  ``activation`` "clamped": with
     g = min(gate_e h_t, limit) and u = clamp(up_e h_t, -limit, limit) an expert is down_e( g sigmoid(1.702 g) (u + 1) ).
     The (token, choice) pairs are sorted by expert on the device and every expert multiplies its own rows (csrc/routed.cu):
-    nothing comes back to the host."""
+    nothing comes back to the host.  ``activation`` "relu2": experts without a gate; ``gate_up`` is then [experts, F, H] and
+    an expert is down_e( relu(up_e h_t)^2 ).  ``identity``: choices in [experts, experts + identity) stand for experts that
+    return their input: out[t] += weight * h_t."""
     _need_cuda(h, chosen, weights, gate_up, down, shared)
     T, H = h.shape
     experts, F2, _ = gate_up.shape
-    F, top = F2 // 2, chosen.shape[1]
-    if tuple(gate_up.shape) != (experts, 2 * F, H) or tuple(down.shape) != (experts, H, F) or gate_up.dtype != h.dtype \
+    single = activation in ROUTED_SINGLE
+    F, top = (F2 if single else F2 // 2), chosen.shape[1]
+    if tuple(gate_up.shape) != (experts, F if single else 2 * F, H) or tuple(down.shape) != (experts, H, F) or gate_up.dtype != h.dtype \
             or down.dtype != h.dtype or not (gate_up.is_contiguous() and down.is_contiguous() and h.is_contiguous()) \
             or chosen.dtype != torch.int32 or weights.dtype != torch.float32 \
             or (shared is not None and (shared.dtype != h.dtype or shared.shape != h.shape or not shared.is_contiguous())):
         raise ValueError("routed_experts: shapes or dtypes do not fit")
-    if activation not in ("silu", "clamped") or (activation == "clamped" and not limit > 0.0):
-        raise ValueError("routed_experts: the activation is 'silu' or 'clamped' with a positive limit")
+    if activation not in ("silu", "clamped", "relu2") or (activation == "clamped" and not limit > 0.0):
+        raise ValueError("routed_experts: the activation is 'silu', 'relu2' or 'clamped' with a positive limit")
     limit = float(limit) if activation == "clamped" else 0.0
-    if routed_tcgen05_ok(h, T * top, H, F):
-        return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit)
+    if routed_tcgen05_ok(h, T * top, H, F) and not single:
+        return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit, single, identity)
     lib = _core()
     need = lib.fe_routed_experts_workspace(_c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)))
     work = torch.empty(need, dtype=torch.uint8, device=h.device)
     out = torch.empty((T, H), dtype=h.dtype, device=h.device)
     _run(lib, "fe_routed_experts", _ptr(h), _ptr(chosen), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(shared), _ptr(out),
          _ptr(work), _c_ll(need), _c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)),
-         _c_float(limit), _ptr(status_word(h.device)), _stream())
+         _c_float(limit), _ptr(status_word(h.device)), _c_int(1 if single else 0), _c_int(identity), _stream())
     return out
 
 
