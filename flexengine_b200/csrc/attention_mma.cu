@@ -6,7 +6,9 @@
 // t <= p (and t > p - window when window > 0; t in the chunk of -window positions that holds p when window < 0); query
 // head h reads key/value head h / (nq / nkv).  ``sink``: the softmax starts as if a key of score 0 and value 0 had been
 // seen (running maximum 0, running sum 1), which adds 1 to its denominator; of the blocks and warps that share a row's
-// keys, the first one does.
+// keys, the first one does.  ``mode`` carries the sink in bit 0; bit 1 asks for sigmoid weights instead of a softmax: a
+// visible key weighs sigmoid(score + head_bias[head]), nothing is normalised over the keys, and the parts of a row that
+// blocks and warps share are plainly added.
 //
 // Both kernels walk the keys in tiles of 32 aligned to position 0.  A tile's keys and values are
 // gathered page by page with 16-byte asynchronous copies (cp.async) into a ring of shared-memory
@@ -119,7 +121,8 @@ __device__ __forceinline__ void copy_rows(bf16* ks, bf16* vs, const KvSource& sr
 template <int DMAX, bool UPPER, int KEYS = TK>
 __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, const unsigned (*qfrag)[4],
                                              float (*o)[4], float* m, float* l, int first_key, int d,
-                                             float scale_log2, int pos0, int pos1, int lo0, int lo1, bool masked) {
+                                             float scale_log2, int pos0, int pos1, int lo0, int lo1, bool masked,
+                                             bool sigmoid = false, float bias0 = 0.f, float bias1 = 0.f) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     const int mat = lane >> 3, mrow = lane & 7;
     float s[KEYS / 8][4];
@@ -152,6 +155,19 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
             }
         }
     }
+    if (sigmoid) {
+        // no softmax: the weight of a key is 1 / (1 + 2^-(score + bias)) in log2 units; a masked key (-inf) weighs 0, and
+        // the running maximum and sum stay as they were set (0 and, in one place a row, 1)
+#pragma unroll
+        for (int j = 0; j < KEYS / 8; ++j) {
+            s[j][0] = __frcp_rn(1.f + ex2(-fmaf(s[j][0], scale_log2, bias0)));
+            s[j][1] = __frcp_rn(1.f + ex2(-fmaf(s[j][1], scale_log2, bias0)));
+            if (UPPER) {
+                s[j][2] = __frcp_rn(1.f + ex2(-fmaf(s[j][2], scale_log2, bias1)));
+                s[j][3] = __frcp_rn(1.f + ex2(-fmaf(s[j][3], scale_log2, bias1)));
+            }
+        }
+    } else {
     float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
     for (int j = 0; j < KEYS / 8; ++j) {
@@ -185,6 +201,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
         }
     }
     l[0] += sum0; l[1] += sum1;                       // per-thread partial sums of the rows
+    }
     {
         // row = kk*16 + (mat&1)*8 + mrow, 16-byte chunk = np*2 + (mat>>1)
         const bf16* vbase = vs + ((mat & 1) * 8 + mrow) * pitch<DMAX>() + (mat >> 1) * 8;
@@ -261,9 +278,11 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
                     const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv, int d, int ps,
-                    int num_pages, float scale_log2, int window, int sink, int* __restrict__ status) {
+                    int num_pages, float scale_log2, int window, int mode, int* __restrict__ status,
+                    const float* __restrict__ head_bias) {
     griddep_wait();
     griddep_launch_dependents();
+    const bool sink = mode & 1, sigmoid = mode & 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ long long offs[TK];
     __shared__ long long first_offs[STAGES - 1][TK];
@@ -312,6 +331,17 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         m[0] = m[1] = 0.f;
         if (t == 0) l[0] = l[1] = 1.f;              // the four threads of a row add their sums up later
     }
+    float bias0 = 0.f, bias1 = 0.f;
+    if (sigmoid) {
+        // every part of a row carries maximum 0, and the first warp of each block sum 1: the merges below then add the
+        // parts up unweighted and divide a block's part by 1
+        m[0] = m[1] = 0.f;
+        if (warp == 0 && t == 0) l[0] = l[1] = 1.f;
+        if (head_bias) {
+            if (g < G) bias0 = head_bias[kvh * G + g] * 1.4426950408889634f;
+            if (UPPER && g + 8 < G) bias1 = head_bias[kvh * G + g + 8] * 1.4426950408889634f;
+        }
+    }
 
     for (int it = 0; it < n_tiles; ++it) {
         // the stage of tile it - 1 is free (both warps finished it): tile it + AHEAD goes there
@@ -330,7 +360,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         const bf16* sp = smem + (it % STAGES) * 2 * TILE + warp * DECODE_KEYS * pitch<DMAX>();
         const int first = (t_begin + it) * TK + warp * DECODE_KEYS;
         compute_tile<DMAX, UPPER, DECODE_KEYS>(sp, sp + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
-                                               first + DECODE_KEYS - 1 > pos || first < lo);
+                                               first + DECODE_KEYS - 1 > pos || first < lo, sigmoid, bias0, bias1);
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -427,7 +457,9 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                 sum += w;
                 acc += w * val[s2];
             }
-            out[(size_t)tok * out_stride + (size_t)(kvh * G + row) * d + col] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+            // sigmoid weights: every split's part has weight 1 and the parts are added, not averaged
+            out[(size_t)tok * out_stride + (size_t)(kvh * G + row) * d + col] =
+                __float2bfloat16_rn(sigmoid ? acc : (sum > 0.f ? acc / sum : 0.f));
         }
         cluster_barrier();                        // nobody leaves while its shared memory may still be read
     }
@@ -442,7 +474,7 @@ constexpr int COMBINE_MAX_GROUPS = 8;        // sets of threads that share the s
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
                                       int nq, int d, int splits, int groups, int requests,
-                                      const void* __restrict__ upcoming, long long upcoming_bytes) {
+                                      const void* __restrict__ upcoming, long long upcoming_bytes, int added) {
     if ((int)blockIdx.y >= requests) {
         // rows of blocks beyond the requests: the merge barely touches memory, so they start the matrix that the
         // next kernel streams (the output projection) into L2
@@ -478,7 +510,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
             sum += s < splits ? w : 0.f;
         }
         sum = warp_sum(sum);
-        if (threadIdx.x == 0) inv_total = sum > 0.f ? 1.f / sum : 0.f;
+        // ``added`` (sigmoid weights): the parts, each of weight 1, are added and not averaged
+        if (threadIdx.x == 0) inv_total = added ? 1.f : (sum > 0.f ? 1.f / sum : 0.f);
     }
     __syncthreads();
     // ``groups`` sets of threads share the splits out among them (split s goes to set s % groups), so that a
@@ -525,9 +558,11 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32)
 paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                      const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
                      int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv,
-                     int d, int ps, int num_pages, float scale_log2, int window, int sink, int* __restrict__ status) {
+                     int d, int ps, int num_pages, float scale_log2, int window, int mode, int* __restrict__ status,
+                     const float* __restrict__ head_bias) {
     griddep_wait();
     griddep_launch_dependents();
+    const bool sink = mode & 1, sigmoid = mode & 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ long long offs[2][PREFILL_KEYS];
     constexpr int THREADS = PREFILL_WARPS * 32;
@@ -571,10 +606,12 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
-    if (sink) {
+    if (sink || sigmoid) {
         m[0] = m[1] = 0.f;
         if (t == 0) l[0] = l[1] = 1.f;              // the four threads of a row add their sums up later
     }
+    const float bias0 = (sigmoid && head_bias) ? head_bias[head0] * 1.4426950408889634f : 0.f;
+    const float bias1 = (sigmoid && head_bias) ? head_bias[head1] * 1.4426950408889634f : 0.f;
 
     // this warp's rows: the first and last position any of them has, and the widest window edge
     const int w_first = m_block + warp * 16, w_last = min(rows - 1, w_first + 15);
@@ -598,7 +635,7 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
                 // rows differ in what they see only near the diagonal and the window edge
                 const bool masked = first + TK - 1 > w_pos_min || first < w_lo_max || !(v0 && v1);
                 compute_tile<DMAX, true>(st + sub * TK * pitch<DMAX>(), st + STAGE + sub * TK * pitch<DMAX>(), qfrag, o, m,
-                                         l, first, d, scale_log2, pos0, pos1, lo0, lo1, masked);
+                                         l, first, d, scale_log2, pos0, pos1, lo0, lo1, masked, sigmoid, bias0, bias1);
             }
         }
         // offsets of stage it + 2 go where those of stage ``it`` were: all copies of stage ``it``'s
@@ -670,7 +707,7 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
                                             const void* kc, const void* vc, const int* block_table, int bt_stride,
                                             const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
                                             int num_pages, float scale, int window, int sink, int splits, const void* upcoming,
-                                            long long upcoming_bytes, int* status, cudaStream_t stream) {
+                                            long long upcoming_bytes, int* status, const float* head_bias, cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
     FE_REQUIRE(splits >= 1 && splits <= MAX_SPLITS_SHARED && requests >= 0,
@@ -686,7 +723,7 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
         if (allow_smem(paged_decode_kernel<DMAX, UPPER>, decode_smem<DMAX>(), "paged_decode")) return 1;          \
         fe::launch(paged_decode_kernel<DMAX, UPPER>, grid, DECODE_WARPS * 32, decode_smem<DMAX>(), stream,                               \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
-            block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);  \
+            block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status, head_bias);  \
     } while (0)
     const bool upper = nq / nkv > 8;
     if (d <= 64) { if (upper) FE_DECODE(64, true); else FE_DECODE(64, false); }
@@ -700,7 +737,7 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
         const int cols = d >= 128 ? 128 : 64;
         const int groups = splits >= 64 ? 8 : splits >= 32 ? 4 : splits >= 16 ? 2 : 1;
         fe::launch(decode_combine_kernel, dim3(nq, requests + extra), cols * groups, 0, stream,
-            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits, groups, requests, upcoming, upcoming_bytes);
+            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits, groups, requests, upcoming, upcoming_bytes, sink & 2);
         return fe_check_launch("paged_decode combine");
     }
     return 0;
@@ -761,7 +798,7 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
                                        const void* kc, const void* vc, const int* block_table, int bt_stride,
                                        const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
                                        int num_pages, float scale, int window, int sink, int splits, int* status,
-                                       cudaStream_t stream) {
+                                       const float* head_bias, cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
     FE_REQUIRE(splits >= 1 && splits <= CLUSTER_MAX_SPLITS && requests >= 0,
@@ -800,7 +837,7 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
         cfg.dynamicSmemBytes = decode_smem<DMAX>(STAGES);                                                              \
         const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,     \
             (float*)nullptr, (float*)nullptr, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, \
-            nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);                                              \
+            nq, nkv, d, ps, num_pages, scale_log2, window, sink, status, head_bias);                                   \
         FE_REQUIRE(err == cudaSuccess, "paged_decode (cluster of %d): %s", splits, cudaGetErrorString(err));           \
     } while (0)
     const bool upper = nq / nkv > 8;
@@ -818,14 +855,14 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
                                    int num_pages, float scale, int window, int splits, int* status,
                                    cudaStream_t stream) {
     return fe_paged_decode_mma_upcoming(q, q_stride, out, out_stride, scratch, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                        requests, nq, nkv, d, ps, num_pages, scale, window, 0, splits, nullptr, 0, status, stream);
+                                        requests, nq, nkv, d, ps, num_pages, scale, window, 0, splits, nullptr, 0, status, nullptr, stream);
 }
 
 extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                     const void* kc, const void* vc, const int* block_table, int bt_stride,
                                     const int* cu_q, const int* q_start, int requests, int max_q_len, int nq, int nkv,
                                     int d, int ps, int num_pages, float scale, int window, int sink, int* status,
-                                    cudaStream_t stream) {
+                                    const float* head_bias, cudaStream_t stream) {
     if (check_common("paged_prefill", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(requests >= 0 && max_q_len >= 0, "paged_prefill: bad request count or length");
     if (requests == 0 || max_q_len == 0) return 0;
@@ -839,7 +876,7 @@ extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out
         if (allow_smem(paged_prefill_kernel<DMAX>, prefill_smem<DMAX>(), "paged_prefill")) return 1;           \
         fe::launch(paged_prefill_kernel<DMAX>, grid, PREFILL_WARPS * 32, prefill_smem<DMAX>(), stream,                 \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table,  \
-            bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);            \
+            bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status, head_bias); \
     } while (0)
     if (d <= 64) FE_PREFILL(64);
     else if (d <= 128) FE_PREFILL(128);

@@ -231,14 +231,39 @@ __device__ __forceinline__ float row_exp(const unsigned* r, unsigned p_addr, int
     return sum.x + sum.y;
 }
 
+// Sigmoid weights instead of a softmax: P = 1 / (1 + 2^-(s scale + bias)) as bfloat16 pairs over the scores' own columns;
+// nothing is summed, a masked key weighs 0.
+template <bool MASKED>
+__device__ __forceinline__ void row_sigmoid(const unsigned* r, unsigned p_addr, int hi, int lo, float scale_log2, float bias) {
+    const float2 scale2 = make_float2(-scale_log2, -scale_log2), bias2 = make_float2(-bias, -bias);
+#pragma unroll
+    for (int c = 0; c < KEYS; c += 32) {
+        unsigned packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int k = c + 2 * i;
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), scale2, bias2);
+            float2 e = make_float2(__frcp_rn(1.f + ex2(t.x)), __frcp_rn(1.f + ex2(t.y)));
+            if (MASKED) {
+                if (k > hi || k < lo) e.x = 0.f;
+                if (k + 1 > hi || k + 1 < lo) e.y = 0.f;
+            }
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(e.x, e.y);
+            packed[i] = *reinterpret_cast<const unsigned*>(&pair);
+        }
+        tmem_store16(p_addr + (c >> 1), packed);
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                              const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                              const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ q_start, int nq, int nkv, int ps, int num_pages, float scale_log2,
-                             int window, int sink, int splits, float* __restrict__ part_o, float* __restrict__ part_lse,
-                             int* __restrict__ status) {
+                             int window, int mode, int splits, float* __restrict__ part_o, float* __restrict__ part_lse,
+                             int* __restrict__ status, const float* __restrict__ head_bias) {
+    const bool sink = mode & 1, sigmoid = mode & 2;         // bit 1: sigmoid(score + head_bias[head]) instead of a softmax
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], s_ready[2][2], p_ready[2][2], pv_done[2], o_final[2];
     __shared__ long long offs[2][KEYS];
@@ -430,6 +455,9 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         const int pos_min = __reduce_min_sync(FULL, pos), lo_max = __reduce_max_sync(FULL, row_lo);
         float m_ref = -CUDART_INF_F, row_sum = 0.f;
         if (sink && split == 0) { m_ref = 0.f; row_sum = 1.f; }
+        // sigmoid weights: nothing is normalised; every split's share of a row stands with sum 1 and the merge adds them
+        if (sigmoid) { m_ref = 0.f; row_sum = 1.f; }
+        const float bias = (sigmoid && head_bias && valid) ? head_bias[head] * 1.4426950408889634f : 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             ok = __all_sync(FULL, mbar_wait(&s_ready[ti][j & 1], (j >> 1) & 1, &give_up));
@@ -445,6 +473,14 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             const int key0 = (t_begin + j) * KEYS;
             const bool unmasked = key0 + KEYS - 1 <= pos_min && key0 >= lo_max;      // for the whole warp
             const int rel_hi = pos - key0, rel_lo = row_lo - key0;
+            if (sigmoid) {
+                if (unmasked) row_sigmoid<false>(raw, s_addr, rel_hi, rel_lo, scale_log2, bias);
+                else row_sigmoid<true>(raw, s_addr, rel_hi, rel_lo, scale_log2, bias);
+                tmem_store_wait();
+                tc_fence_before();
+                mbar_arrive(&p_ready[ti][j & 1]);
+                continue;
+            }
             const float mx = unmasked ? row_max<false>(raw, rel_hi, rel_lo) : row_max<true>(raw, rel_hi, rel_lo);
             const float m_new = fmaxf(m_ref, mx * scale_log2);
             if (__any_sync(FULL, m_new > m_ref + RESCALE_STEP)) {
@@ -542,7 +578,7 @@ constexpr int MAX_SPLITS = 32;                       // the merge keeps one spli
 template <int D>
 __global__ void __launch_bounds__(128)
 prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
-                     long long out_stride, int nq, int splits, long long items) {
+                     long long out_stride, int nq, int splits, long long items, int added) {
     griddep_wait();
     griddep_launch_dependents();
     const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -554,7 +590,7 @@ prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__
     const float mx = warp_max(lse);
     const float w = mx == -CUDART_INF_F ? 0.f : exp2f(lse - mx);       // 0 for a split that saw no key of this row
     const float total = warp_sum(w);
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    const float inv = added ? 1.f : (total > 0.f ? 1.f / total : 0.f);      // added (sigmoid weights): shares of weight 1, summed
     constexpr int CHUNKS = D / 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < splits; ++s) {
@@ -576,7 +612,7 @@ template <int D>
 int launch(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
            const int* block_table, int bt_stride, const int* cu_q, const int* q_start, int requests, int max_q_len, int nq,
            int nkv, int ps, int num_pages, float scale, int window, int sink, int splits, float* scratch, long long total_tokens,
-           int* status, cudaStream_t stream) {
+           int* status, const float* head_bias, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * (2 * Q_BLOCK + 2 * KV_STAGES * KV_BLOCK) + 1024;
     const cudaError_t err = cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "paged_prefill_tcgen05: %s", cudaGetErrorString(err));
@@ -588,13 +624,13 @@ int launch(const void* q, long long q_stride, void* out, long long out_stride, c
     float* part_lse = splits > 1 ? scratch + (size_t)total_tokens * nq * splits * D : nullptr;
     fe::launch(paged_prefill_tcgen05_kernel<D>, dim3((unsigned)tiles, nkv, requests), THREADS, smem, stream, (const bf16*)q, q_stride,
                (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, nq, nkv, ps,
-               num_pages, scale * LOG2E, window, sink, splits, part_o, part_lse, status);
+               num_pages, scale * LOG2E, window, sink, splits, part_o, part_lse, status, head_bias);
     if (fe_check_launch("paged_prefill_tcgen05")) return 1;
     if (splits > 1) {
         const long long items = total_tokens * nq;
         FE_REQUIRE((items + 3) / 4 <= 2147483647LL, "paged_prefill_tcgen05: merge grid too large");
         fe::launch(prefill_merge_kernel<D>, dim3((unsigned)((items + 3) / 4)), 128, 0, stream, (const float*)part_o,
-                   (const float*)part_lse, (bf16*)out, out_stride, nq, splits, items);
+                   (const float*)part_lse, (bf16*)out, out_stride, nq, splits, items, sink & 2);
         return fe_check_launch("paged_prefill_tcgen05 merge");
     }
     return 0;
@@ -614,7 +650,7 @@ extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void*
                                         const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                         const int* q_start, int requests, int max_q_len, int nq, int nkv, int d, int ps,
                                         int num_pages, float scale, int window, int sink, int splits, void* scratch,
-                                        long long total_tokens, int* status, cudaStream_t stream) {
+                                        long long total_tokens, int* status, const float* head_bias, cudaStream_t stream) {
     FE_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "paged_prefill_tcgen05: bad head counts %d/%d", nq, nkv);
     FE_REQUIRE(d == 64 || d == 128, "paged_prefill_tcgen05: head size %d; this kernel takes 64 and 128", d);
     FE_REQUIRE(ps > 0 && num_pages > 0, "paged_prefill_tcgen05: bad page size or page count");
@@ -627,7 +663,7 @@ extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void*
     if (requests == 0 || max_q_len == 0) return 0;
     if (d == 64)
         return launch<64>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv,
-                          ps, num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, stream);
+                          ps, num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, head_bias, stream);
     return launch<128>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv, ps,
-                       num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, stream);
+                       num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, head_bias, stream);
 }

@@ -33,7 +33,8 @@ namespace {
 constexpr int WARPS_USUAL = 8, WARPS_NARROW = 16;
 constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_RESID = 4, EPI_GEGLU = 5 };   // 5: gated, the tanh form of GELU
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_RESID = 4, EPI_GEGLU = 5, EPI_RELU2 = 6 };   // 5: gated, the tanh form of GELU
+constexpr int ACT_RELU2 = 3;            // ``gate_act`` of the bfloat16 epilogue: the square of relu(product), no gate (entry code 6)
 
 // The gate's function of the gated epilogue: 0 silu, 1 the tanh form of GELU, z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 __device__ __forceinline__ float gate_function(float z, int act) {
@@ -377,6 +378,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) v += red[w][(r * NT * 8 + m) * 16 + row];
             if (scale.sumsq != nullptr) v *= row_scale[m];
+            if (EPI == EPI_BF16 && gate_act == ACT_RELU2) v = v > 0.f ? v * v : 0.f;
             if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
             else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
         }
@@ -431,7 +433,7 @@ static int check_scale(const char* what, const float* sumsq, int sumsq_tiles, in
 }
 
 // epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I]; 5 the
-// same with the tanh form of GELU as the gate's function.
+// same with the tanh form of GELU as the gate's function; 6 out = relu(x W^T)^2 as bfloat16 [M, N].
 // ``sumsq`` (may be null): see check_scale.
 extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
                                      const float* sumsq, int sumsq_tiles, float eps, const void* next, long long next_bytes,
@@ -444,6 +446,7 @@ extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, in
     const RowScale scale{sumsq, sumsq_tiles, eps, K, next, next_bytes};
     if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
+    if (epilogue == EPI_RELU2) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale, ACT_RELU2);
     if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
         FE_REQUIRE(N % 2 == 0, "skinny_gemm: a gated epilogue needs an even number of weight rows, got %d", N);
         return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream, QkvEpilogue{}, ResidEpilogue{}, scale, epilogue == EPI_GEGLU ? 1 : 0);

@@ -38,7 +38,8 @@ constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr long long WAIT_LIMIT = 4000000000LL;      // clock cycles
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_GEGLU = 5 };      // 5: the gated epilogue with the tanh form of GELU
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_GEGLU = 5, EPI_RELU2 = 6 };      // 5: the gated epilogue with the tanh form of GELU
+constexpr int ACT_RELU2 = 3;            // ``gate_act`` of the bfloat16 epilogue: the square of relu(product), no gate (entry code 6)
 
 // The gate's function of the gated epilogue: 0 silu, z / (1 + exp(-z)); 1 the tanh form of GELU,
 // z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
@@ -275,6 +276,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = gated_value(v[j], u[j], gate_act, gate_limit);
                 }
+                if (EPI == EPI_BF16 && gate_act == ACT_RELU2) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] * v[j] : 0.f;
+                }
                 if (row < row_end && EPI == EPI_F32) {
                     float* dst = reinterpret_cast<float*>(out_raw) + (size_t)row * N_out + n0 + c;
                     if (n0 + c + 32 <= N_out && (N_out & 3) == 0) {
@@ -363,13 +368,14 @@ int launch(const void* x, const void* W, void* out, int M, int N, int K, int* st
 }  // namespace
 
 // epilogue 0: out bfloat16 [M, N]; 2: SwiGLU, W is [N = 2 I, K] (gate rows, then up rows), out bfloat16 [M, I]; 5: the same
-// with the tanh form of GELU as the gate's function.
+// with the tanh form of GELU as the gate's function; 6: out = relu(x W^T)^2 as bfloat16 [M, N].
 extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K, int epilogue, int* status,
                                cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     FE_REQUIRE(K % 8 == 0, "gemm_tcgen05: K = %d must be a multiple of 8 (rows must start on 16-byte boundaries)", K);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, status, stream);
+    if (epilogue == EPI_RELU2) return launch<EPI_BF16>(x, W, out, M, N, K, status, stream, nullptr, nullptr, nullptr, nullptr, 0, ACT_RELU2);
     if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
         FE_REQUIRE(N % 2 == 0, "gemm_tcgen05: a gated epilogue needs an even number of weight rows, got %d", N);
         return launch<EPI_SWIGLU>(x, W, out, M, N, K, status, stream, nullptr, nullptr, nullptr, nullptr, 0, epilogue == EPI_GEGLU ? 1 : 0);
@@ -380,7 +386,8 @@ extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, i
 // The grouped form: x [rows, K] sorted by expert, W [experts * N, K] (every expert's N rows; for SwiGLU its gate rows,
 // then its up rows), the row tiles of 128 from a list on the device (tiles[0] of them: tile_expert, tile_row0; offsets
 // [experts + 1] are the experts' row ranges).  epilogue 1: out float [rows, N]; 2: SwiGLU, out bfloat16 [rows, N / 2]; with
-// ``limit`` > 0 the gated epilogue is the clamped one (see gated_value).
+// ``limit`` > 0 the gated epilogue is the clamped one (see gated_value); 6: experts without a gate, out = relu(product)^2 as
+// bfloat16 [rows, N].
 extern "C" int fe_gemm_tcgen05_grouped(const void* x, const void* W, void* out, int rows, int experts, int N, int K, int epilogue,
                                        const int* tiles, const int* tile_expert, const int* tile_row0, const int* offsets,
                                        float limit, int* status, cudaStream_t stream) {
@@ -390,6 +397,8 @@ extern "C" int fe_gemm_tcgen05_grouped(const void* x, const void* W, void* out, 
     FE_REQUIRE(tiles && tile_expert && tile_row0 && offsets, "gemm_tcgen05 (grouped): the tile list is missing");
     const long long w_rows_total = (long long)experts * N;
     if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total);
+    if (epilogue == EPI_RELU2)
+        return launch<EPI_BF16>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total, ACT_RELU2);
     if (epilogue == EPI_SWIGLU) {
         FE_REQUIRE(N % 2 == 0, "gemm_tcgen05 (grouped): SwiGLU needs an even number of weight rows, got %d", N);
         return launch<EPI_SWIGLU>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total,

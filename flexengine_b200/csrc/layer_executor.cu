@@ -31,15 +31,17 @@ extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void*
                                         const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                         const int* q_start, int requests, int max_q_len, int nq, int nkv, int d, int ps,
                                         int num_pages, float scale, int window, int sink, int splits, void* scratch,
-                                        long long total_tokens, int* status, cudaStream_t stream);
+                                        long long total_tokens, int* status, const float* head_bias, cudaStream_t stream);
 extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                                     const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                     const int* q_start, int requests, int max_q_len, int nq, int nkv, int d, int ps,
-                                    int num_pages, float scale, int window, int sink, int* status, cudaStream_t stream);
+                                    int num_pages, float scale, int window, int sink, int* status, const float* head_bias,
+                                    cudaStream_t stream);
 extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                                        const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                        const int* q_start, int requests, int nq, int nkv, int d, int ps, int num_pages,
-                                       float scale, int window, int sink, int splits, int* status, cudaStream_t stream);
+                                       float scale, int window, int sink, int splits, int* status, const float* head_bias,
+                                       cudaStream_t stream);
 extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
                                    const void* kc, const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                    const int* q_start, int requests, int nq, int nkv, int d, int ps, int num_pages,
@@ -193,7 +195,7 @@ extern "C" int fe_layer_forward(const FeLayer* layer, const FeStep* step, void* 
         case 0:
             rc = fe_paged_decode_cluster(qkv, Wq, heads, out_stride, k_cache, v_cache, S.block_table, S.bt_stride, S.cu_q,
                                          S.q_start, S.R, L.nq, L.nkv, L.d, S.page_size, S.num_pages, L.scale, L.window, 0, S.splits,
-                                         S.status, stream);
+                                         S.status, nullptr, stream);
             break;
         case 1:
             rc = fe_paged_decode_mma(qkv, Wq, heads, out_stride, S.attention_scratch, k_cache, v_cache, S.block_table,
@@ -203,12 +205,12 @@ extern "C" int fe_layer_forward(const FeLayer* layer, const FeStep* step, void* 
         case 2:
             rc = fe_paged_prefill_tcgen05(qkv, Wq, heads, out_stride, k_cache, v_cache, S.block_table, S.bt_stride, S.cu_q,
                                           S.q_start, S.R, S.max_q_len, L.nq, L.nkv, L.d, S.page_size, S.num_pages, L.scale,
-                                          L.window, 0, S.splits, S.attention_scratch, T, S.status, stream);
+                                          L.window, 0, S.splits, S.attention_scratch, T, S.status, nullptr, stream);
             break;
         case 3:
             rc = fe_paged_prefill_mma(qkv, Wq, heads, out_stride, k_cache, v_cache, S.block_table, S.bt_stride, S.cu_q,
                                       S.q_start, S.R, S.max_q_len, L.nq, L.nkv, L.d, S.page_size, S.num_pages, L.scale, L.window,
-                                      0, S.status, stream);
+                                      0, S.status, nullptr, stream);
             break;
         default:
             FE_REQUIRE(false, "layer_forward: unknown attention kind %d", S.attention);

@@ -347,7 +347,7 @@ def tcgen05_ok(x, w) -> bool:
 
 def gemm_tcgen05(x, w, epilogue: int = EPI_BF16):
     """x [M, K] times w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator);
-    epilogue EPI_BF16, EPI_SWIGLU or EPI_GEGLU.  See csrc/gemm_tcgen05.cu."""
+    epilogue EPI_BF16, EPI_SWIGLU, EPI_GEGLU or EPI_RELU2.  See csrc/gemm_tcgen05.cu."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
@@ -496,10 +496,14 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
 ATTENTION_SINK, ATTENTION_SIGMOID = 1, 2       # bits of the attention kernels' mode
 
 
+def _attention_mode(sink: bool, sigmoid: bool) -> int:
+    return (ATTENTION_SINK if sink else 0) | (ATTENTION_SIGMOID if sigmoid else 0)
+
+
 def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, token_request, T, nq, nkv, d,
                          page_size, scale, window, sink=False, sigmoid=False, head_bias=None):
     out = torch.empty((T, nq * d), dtype=k_cache.dtype, device=k_cache.device)
-    mode = (ATTENTION_SINK if sink else 0) | (ATTENTION_SIGMOID if sigmoid else 0)
+    mode = _attention_mode(sink, sigmoid)
     _run(_core(), "fe_paged_attention_simt", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _ptr(token_request), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size),
@@ -564,7 +568,7 @@ def decode_splits(requests: int, nkv: int, max_ctx_len: int, sms: int | None = N
 
 
 def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
-                     scale, window, splits, out=None, upcoming=None, sink=False):
+                     scale, window, splits, out=None, upcoming=None, sink=False, sigmoid=False, head_bias=None):
     """Tensor-core decode attention (one token per request), keys split ``splits`` ways.  ``upcoming``: the
     matrix that the next kernel streams (the output projection); extra blocks of the merge kernel ask for its
     start to be brought into L2."""
@@ -576,9 +580,9 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     _run(lib, "fe_paged_decode_mma_upcoming", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
          _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _c_int(requests), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(splits),
+         _c_float(scale), _c_int(window), _c_int(_attention_mode(sink, sigmoid)), _c_int(splits),
          *_upcoming(upcoming, requests, UPCOMING_BYTES_MERGE),
-         _ptr(status_word(k_cache.device)), _stream())
+         _ptr(status_word(k_cache.device)), _ptr(head_bias), _stream())
     return out
 
 
@@ -623,7 +627,7 @@ def decode_cluster_splits(splits: int, max_ctx_len: int, clusters: int = 0, resi
 
 
 def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
-                         scale, window, splits, out=None, sink=False):
+                         scale, window, splits, out=None, sink=False, sigmoid=False, head_bias=None):
     """Decode attention with the splits of each (request, key/value head) as one thread-block cluster that merges
     its partial results through distributed shared memory: one launch, no scratch memory; splits <= 16."""
     if out is None:
@@ -631,18 +635,19 @@ def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_sta
     _run(_bf16(), "fe_paged_decode_cluster", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window),
-         _c_int(1 if sink else 0), _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
+         _c_int(_attention_mode(sink, sigmoid)), _c_int(splits), _ptr(status_word(k_cache.device)), _ptr(head_bias), _stream())
     return out
 
 
 def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
-                      page_size, scale, window, sink=False):
+                      page_size, scale, window, sink=False, sigmoid=False, head_bias=None):
     """Tensor-core attention for portions of any length (decoded tokens are portions of one)."""
     out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
     _run(_bf16(), "fe_paged_prefill_mma", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _ptr(status_word(k_cache.device)), _stream())
+         _c_float(scale), _c_int(window), _c_int(_attention_mode(sink, sigmoid)), _ptr(status_word(k_cache.device)), _ptr(head_bias),
+         _stream())
     return out
 
 
@@ -686,7 +691,7 @@ def prefill_splits(lengths, starts, nq, nkv, window=0, sms: int | None = None) -
 
 
 def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
-                          page_size, scale, window, splits=1, sink=False):
+                          page_size, scale, window, splits=1, sink=False, sigmoid=False, head_bias=None):
     """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128.
     ``splits`` > 1 shares the keys of each pair of row tiles out over that many blocks and merges their results."""
     out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
@@ -694,8 +699,8 @@ def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_st
     _run(_bf16(), "fe_paged_prefill_tcgen05", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(splits), _ptr(part),
-         _c_ll(T), _ptr(status_word(k_cache.device)), _stream())
+         _c_float(scale), _c_int(window), _c_int(_attention_mode(sink, sigmoid)), _c_int(splits), _ptr(part),
+         _c_ll(T), _ptr(status_word(k_cache.device)), _ptr(head_bias), _stream())
     return out
 
 
@@ -721,7 +726,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         _need_cuda(head_bias)
         if not sigmoid or head_bias.dtype != torch.float32 or head_bias.numel() != nq:
             raise ValueError("paged_attention: a head bias goes with sigmoid weights and is float32 [heads]")
-    if qkv.dtype == torch.float32 or d > 256 or sigmoid:          # the tensor-core kernels take head sizes up to 256
+    if qkv.dtype == torch.float32 or d > 256:          # the tensor-core kernels take head sizes up to 256
         return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
                                     ctx.token_request, T, nq, nkv, d, page_size, scale, window, sink, sigmoid, head_bias)
     requests = ctx.cu_q.numel() - 1
@@ -733,16 +738,18 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
                                           lambda s: clusters_resident(requests, nq, nkv, d, s))
         if clustered:
             return paged_decode_cluster(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
-                                        nq, nkv, d, page_size, scale, window, clustered, sink=sink)
+                                        nq, nkv, d, page_size, scale, window, clustered, sink=sink, sigmoid=sigmoid, head_bias=head_bias)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
-                                nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming, sink=sink)
+                                nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming, sink=sink, sigmoid=sigmoid,
+                                head_bias=head_bias)
     lengths = getattr(ctx, "host_lengths", None)
     if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d, lengths, getattr(ctx, "host_starts", None)):
         splits = prefill_splits(lengths, ctx.host_starts, nq, nkv, window) if lengths else 1
         return paged_prefill_tcgen05(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                                     ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits, sink=sink)
+                                     ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits, sink=sink, sigmoid=sigmoid,
+                                     head_bias=head_bias)
     return paged_prefill_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                             ctx.max_q_len, nq, nkv, d, page_size, scale, window, sink=sink)
+                             ctx.max_q_len, nq, nkv, d, page_size, scale, window, sink=sink, sigmoid=sigmoid, head_bias=head_bias)
 
 
 # ---- several residual streams, token shift, gated attention, minGRU ---------------------------------------------
@@ -1023,7 +1030,14 @@ def activation(x, kind, params=None):
 
 
 def linear_activated(x, w, kind):
-    """act(x w^T) for an activation without parameters ("relu2", "tanh"): the product, then the activation kernel."""
+    """act(x w^T) for an activation without parameters ("relu2", "tanh").  The square of relu is an epilogue of the
+    weight-streaming kernel (a handful of rows) and of the tcgen05 kernel (a prompt's worth); otherwise the product, then the
+    activation kernel."""
+    if kind == "relu2" and not isinstance(x, Prenormed):
+        if _fits(x, w) == "skinny":
+            return skinny_gemm(x, w, EPI_RELU2)
+        if tcgen05_ok(x, w):
+            return gemm_tcgen05(x, w, EPI_RELU2)
     return activation(linear(x, w), kind)
 
 
@@ -1296,7 +1310,7 @@ def routed_experts(h, chosen, weights, gate_up, down, shared=None, activation="s
     if activation not in ("silu", "clamped", "relu2") or (activation == "clamped" and not limit > 0.0):
         raise ValueError("routed_experts: the activation is 'silu', 'relu2' or 'clamped' with a positive limit")
     limit = float(limit) if activation == "clamped" else 0.0
-    if routed_tcgen05_ok(h, T * top, H, F) and not single:
+    if routed_tcgen05_ok(h, T * top, H, F):
         return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared, limit, single, identity)
     lib = _core()
     need = lib.fe_routed_experts_workspace(_c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)))

@@ -89,7 +89,7 @@ def test_entry_points_take_the_types_their_c_declarations_name():
         called = set(re.findall(r"\bfe_\w+", f.read()))
     assert called and called <= set(declared), called - set(declared)
     restype, args = declared["fe_paged_prefill_tcgen05"]
-    assert restype is ctypes.c_int and len(args) == 25
+    assert restype is ctypes.c_int and len(args) == 26
     assert args[0] is ctypes.c_void_p and args[1] is ctypes.c_longlong and args[17] is ctypes.c_float
     assert declared["fe_static_scratch_bytes"] == (ctypes.c_longlong, [])
     assert declared["fe_last_error"][0] is ctypes.c_char_p and declared["fe_set_pdl"] == (None, [ctypes.c_int])

@@ -555,11 +555,61 @@ def test_sigmoid_weights_in_every_attention_kernel(dtype, shape, lengths):
                                 max_q_len=max(counts), max_ctx_len=most, host_lengths=counts, host_starts=starts)
     bias = (torch.arange(nq, dtype=torch.float32) * 0.9 - 4.0).to(dev)
     scale = d ** -0.5
-    got = ops.paged_attention(q, kc, vc, table, ctx, nq, nkv, d, page, scale, 0, weights="sigmoid", head_bias=bias)
     want = kernel_refs.paged_attention(q, kc, vc, table, ctx, nq, nkv, d, page, scale, 0, weights="sigmoid", head_bias=bias)
-    err = (got.float() - want.float()).abs().max()
-    assert float(err) <= (2e-4 if dtype == "float32" else 3e-2) * max(1.0, float(want.float().abs().max())), f"error {float(err):.3e}"
+    runs = {"as the step would choose": lambda: ops.paged_attention(q, kc, vc, table, ctx, nq, nkv, d, page, scale, 0, weights="sigmoid",
+                                                                     head_bias=bias)}
+    if dtype == "bfloat16":
+        # every tensor-core kernel by name: splits merged in a cluster and by a second kernel, both prefill kernels, split keys
+        common = (q, q.stride(0), kc, vc, table, ctx.cu_q, ctx.q_start)
+        if max(counts) == 1 and nq // nkv <= 16:
+            for splits in (1, 3, 8):
+                runs[f"cluster of {splits}"] = lambda splits=splits: ops.paged_decode_cluster(
+                    *common, R, nq, nkv, d, page, scale, 0, splits, sigmoid=True, head_bias=bias)
+            for splits in (1, 5, 40):
+                runs[f"{splits} splits and a merge"] = lambda splits=splits: ops.paged_decode_mma(
+                    *common, R, nq, nkv, d, page, scale, 0, splits, sigmoid=True, head_bias=bias)
+        runs["mma.sync portions"] = lambda: ops.paged_prefill_mma(*common, T, R, max(counts), nq, nkv, d, page, scale, 0, sigmoid=True,
+                                                                  head_bias=bias)
+        if d in (64, 128):
+            for splits in (1, 4):
+                runs[f"tcgen05 portions, keys split {splits} ways"] = lambda splits=splits: ops.paged_prefill_tcgen05(
+                    *common, T, R, max(counts), nq, nkv, d, page, scale, 0, splits=splits, sigmoid=True, head_bias=bias)
+    for what, run in runs.items():
+        got = run()
+        err = (got.float() - want.float()).abs().max()
+        assert float(err) <= (2e-4 if dtype == "float32" else 3e-2) * max(1.0, float(want.float().abs().max())), f"{what}: error {float(err):.3e}"
     ops.check_status(dev)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,K,N", [(1, 128, 72), (8, 256, 520), (1100, 1024, 520), (2048, 1536, 1000), (37, 96, 40)])
+def test_squared_relu_in_the_products_epilogues(rows, K, N):
+    """The weight-streaming kernel (a handful of rows), the tcgen05 kernel (a prompt's worth) and the product with the
+    activation kernel behind it give the same rows."""
+    from flexengine_b200 import ops
+    x = randn(rows, K, seed=1).to(device="cuda:0", dtype=torch.bfloat16)
+    w = randn(N, K, seed=2, scale=K ** -0.5).to(device="cuda:0", dtype=torch.bfloat16)
+    got = ops.linear_activated(x, w, "relu2")
+    want = kernel_refs.linear_activated(x, w, "relu2")
+    assert (got.float() - want.float()).abs().max() <= 2e-2 * max(1.0, float(want.float().abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,D,F,experts,identity,top", [(700, 1024, 1024, 4, 2, 2), (1500, 1024, 1536, 3, 0, 1), (300, 256, 128, 6, 3, 3)])
+def test_experts_without_a_gate_on_the_grouped_products(T, D, F, experts, identity, top):
+    """Enough rows and wide enough experts for the grouped tcgen05 product (and one shape for the pipelined tiles), with choices
+    that name experts which return their input: those pairs have no row in the sorted order."""
+    from flexengine_b200 import ops
+    gen = torch.Generator().manual_seed(3)
+    h = randn(T, D, seed=4).to(device="cuda:0", dtype=torch.bfloat16)
+    up = randn(experts, F, D, seed=5, scale=D ** -0.5).to(device="cuda:0", dtype=torch.bfloat16)
+    down = randn(experts, D, F, seed=6, scale=F ** -0.5).to(device="cuda:0", dtype=torch.bfloat16)
+    chosen = torch.stack([torch.randperm(experts + identity, generator=gen)[:top] for _ in range(T)]).to(torch.int32).cuda()
+    weights = torch.rand(T, top, generator=gen).cuda()
+    got = ops.routed_experts(h, chosen, weights, up, down, activation="relu2", identity=identity)
+    want = kernel_refs.routed_experts(h, chosen, weights, up, down, activation="relu2", identity=identity)
+    assert (got.float() - want.float()).abs().max() <= 3e-2 * max(1.0, float(want.float().abs().max()))
+    ops.check_status("cuda:0")
 
 
 # ---- whole models -------------------------------------------------------------------------------------------------------
