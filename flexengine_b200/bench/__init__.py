@@ -1,10 +1,10 @@
 """``flexengine bench``: the measurements of this engine as a program of the package.
 
-    flexengine bench [--workload decode|serve-1.5b|long-14b|lengths|fuvozen|fuvuvik|fedutar] [--steps K] [--warmup W] [--kernels] ...
+    flexengine bench [--workload decode|serve-1.5b|long-14b|lengths|fuvozen|fuvuvik|fedutar|rikolix] [--steps K] [--warmup W] [--kernels] ...
 
 ``decode`` (the default) is the headline: decode tokens per second on the Qwen2.5-7B shape at batch 8 after
 2,048-token prompts, with prefill, end-to-end, roofline and batch 1 / 64 beside it; ``--kernels`` adds a table of the
-step's kernels with their achieved fraction of the measured peaks.  ``fuvozen``, ``fuvuvik`` and ``fedutar`` measure those designs beside the closest existing model of
+step's kernels with their achieved fraction of the measured peaks.  ``fuvozen``, ``fuvuvik``, ``fedutar`` and ``rikolix`` measure those designs beside the closest existing model of
 equal size (prefill, decode, and with ``--kernels`` both operation by operation).  The other two workloads drive the whole engine
 (scheduler, page pool, CUDA graphs, overlapped steps) on the 1.5B and 14B shapes.  Every run prints ONE JSON line.
 The reference measures over HTTP (src/flexengine/research/benchmark/runner.py:26-105) and in process
@@ -17,8 +17,8 @@ import argparse
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="flexengine bench", description="Measure the engine on one GPU; prints one JSON line")
-    p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b", "lengths", "fuvozen", "fuvuvik", "fedutar"], default="decode")
-    p.add_argument("--size", choices=["1k", "2k", "4k"], default=None, help="one size of the fuvozen, fuvuvik or fedutar workload instead of all three")
+    p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b", "lengths", "fuvozen", "fuvuvik", "fedutar", "rikolix"], default="decode")
+    p.add_argument("--size", choices=["1k", "2k", "4k"], default=None, help="one size of the fuvozen, fuvuvik, fedutar or rikolix workload instead of all three")
     p.add_argument("--shape", choices=["7b", "1.5b", "14b"], default="7b",
                    help="the model shape of the decode workload (the headline is 7b)")
     p.add_argument("--gpus", type=int, default=1)
@@ -59,7 +59,7 @@ def main(argv=None, reference_arm=None) -> int:
     if args.workload == "lengths":
         from .lengths import run as run_lengths
         return run_lengths(args)
-    if args.workload in ("fuvozen", "fuvuvik", "fedutar"):
+    if args.workload in ("fuvozen", "fuvuvik", "fedutar", "rikolix"):
         from .hybrid import run as run_hybrid
         return run_hybrid(args)
     from .headline import run

@@ -1,6 +1,7 @@
-"""``--workload fuvozen|fuvuvik|fedutar``: prefill and decode throughput of one of these designs at a few sizes that resemble a
+"""``--workload fuvozen|fuvuvik|fedutar|rikolix``: prefill and decode throughput of one of these designs at a few sizes that resemble a
 real model's layers (random weights), beside the closest existing model at equal width, depth and vocabulary (a Qwen2
-decoder; for Fedutar the Fuvozen design, which also has a recurrence with a matrix state and routed experts), and, at one size, an
+decoder; for Fedutar the Fuvozen design, which also has a recurrence with a matrix state and routed experts; for Rikolix the
+Fuvozen design too, which also has attention over a cached latent, routed experts and a dense feed-forward without a gate), and, at one size, an
 operation-by-operation table of both: time, the bytes and flops of the work, and how far each operation is from the
 roofline of the measured peaks (time / max(bytes / copy rate, flops / bf16 rate)).
 
@@ -78,7 +79,32 @@ def fedutar_config(width, layers, vocab, heads):
             "logit_scale": 1.0, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 2, "times": 2}, "layers": stack}
 
 
-DESIGNS = {"fuvozen": ("Fuvozen", fuvozen_config), "fuvuvik": ("Fuvuvik", fuvuvik_config), "fedutar": ("Fedutar", fedutar_config)}
+def rikolix_config(width, layers, vocab, heads):
+    """Layers in turns of four: sigmoid attention (heads of 128 in groups of four, half of a head rotated, values that turn)
+    beside a dense feed-forward of 4 x width; latent attention that makes its latents (heads of 64 + 64 rotated over a latent
+    of 64, a cached row of 128 as in the Fuvozen model beside it; queries through a latent of width / 2) beside 8 experts of
+    ``width`` and 2 that return their input, in two groups of which one is kept, two chosen; latent attention that reads
+    those latents beside a dense feed-forward; latent attention of its own beside experts again."""
+    stack = []
+    latent = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 64, "q_rank": width // 2,
+              "rot": {"base": 10000.0, "dims": 64}, "scale": 128 ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 8, "identity": 2, "top": 2, "groups": {"count": 2, "keep": 1}}}
+    for i in range(layers):
+        turn = i % 4
+        if turn == 0:
+            stack.append({"type": "attention",
+                          "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                    "rot": {"base": 500000.0, "dims": 64}},
+                          "mlp": {"kind": "dense", "ff": 4 * width}})
+        elif turn == 2:
+            stack.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 1), "mlp": {"kind": "dense", "ff": 4 * width}})
+        else:
+            stack.append({"type": "latent_attention", "mixer": dict(latent), "mlp": moe})
+    return {"architecture": "Rikolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": stack}
+
+
+DESIGNS = {"fuvozen": ("Fuvozen", fuvozen_config), "fuvuvik": ("Fuvuvik", fuvuvik_config), "fedutar": ("Fedutar", fedutar_config),
+           "rikolix": ("Rikolix", rikolix_config)}
 
 
 def qwen2_config(width, layers, vocab, heads):
@@ -91,7 +117,7 @@ def qwen2_config(width, layers, vocab, heads):
 
 
 # the model a design is measured beside (default: the Qwen2 decoder)
-BESIDE = {"fedutar": ("fuvozen", "Fuvozen", fuvozen_config)}
+BESIDE = {"fedutar": ("fuvozen", "Fuvozen", fuvozen_config), "rikolix": ("fuvozen", "Fuvozen", fuvozen_config)}
 
 SIZES = {"1k": (1024, 8, 32000, 8), "2k": (2048, 8, 32000, 16), "4k": (4096, 4, 32000, 32)}
 
@@ -127,13 +153,16 @@ class TimedOps:
                     seen.add(t.data_ptr())
                     nbytes += t.numel() * t.element_size()
             flops = 0.0
-            if name in ("linear", "linear_swiglu", "linear_gated") and len(args) >= 2:
+            if name in ("linear", "linear_swiglu", "linear_gated", "linear_activated") and len(args) >= 2:
                 flops = 2.0 * args[0].shape[0] * args[1].shape[0] * args[1].shape[1]
             elif name == "batched_linear":
                 flops = 2.0 * args[0].shape[0] * args[0].shape[1] * args[0].shape[2] * args[1].shape[1]
             elif name == "routed_experts":
                 pairs = args[1].numel()
-                flops = 2.0 * pairs * 3 * (args[3].shape[1] // 2) * args[3].shape[2]
+                if kwargs.get("activation") == "relu2":           # experts without a gate: one matrix up, one down
+                    flops = 2.0 * pairs * 2 * args[3].shape[1] * args[3].shape[2]
+                else:
+                    flops = 2.0 * pairs * 3 * (args[3].shape[1] // 2) * args[3].shape[2]
                 used = min(args[3].shape[0], pairs)
                 nbytes = nbytes - (args[3].numel() + args[4].numel()) * 2 * (1 - used / args[3].shape[0])
             elif name in ("paged_attention",):
@@ -169,7 +198,7 @@ class TimedOps:
                     nbytes += update.y.numel() * update.y.element_size() * 2
                 if kwargs.get("rows") is not None:
                     nbytes = nbytes * kwargs["rows"].numel() / max(1, args[0].shape[1])
-            shapes = "x".join(str(tuple(a.shape)) for a in args[:2] if torch.is_tensor(a)) if name in ("linear", "linear_swiglu", "linear_gated", "batched_linear") else ""
+            shapes = "x".join(str(tuple(a.shape)) for a in args[:2] if torch.is_tensor(a)) if name in ("linear", "linear_swiglu", "linear_gated", "linear_activated", "batched_linear") else ""
             row = self.rows.setdefault(f"{name} {shapes}".strip(), [0, 0.0, 0.0, 0.0])
             row[0] += 1
             row[1] += start.elapsed_time(end) * 1e3
