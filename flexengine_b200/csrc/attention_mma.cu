@@ -68,6 +68,12 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// 1 / x in float (the hardware's approximation, 1 ulp); 1 / inf = 0
+__device__ __forceinline__ float rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // Rows of a stage are PITCH = DMAX + 8 elements apart: the 16 bytes of padding shift consecutive
 // rows by one bank group, so the eight rows an ldmatrix touches never collide.
@@ -160,11 +166,11 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
         // the running maximum and sum stay as they were set (0 and, in one place a row, 1)
 #pragma unroll
         for (int j = 0; j < KEYS / 8; ++j) {
-            s[j][0] = __frcp_rn(1.f + ex2(-fmaf(s[j][0], scale_log2, bias0)));
-            s[j][1] = __frcp_rn(1.f + ex2(-fmaf(s[j][1], scale_log2, bias0)));
+            s[j][0] = rcp(1.f + ex2(-fmaf(s[j][0], scale_log2, bias0)));
+            s[j][1] = rcp(1.f + ex2(-fmaf(s[j][1], scale_log2, bias0)));
             if (UPPER) {
-                s[j][2] = __frcp_rn(1.f + ex2(-fmaf(s[j][2], scale_log2, bias1)));
-                s[j][3] = __frcp_rn(1.f + ex2(-fmaf(s[j][3], scale_log2, bias1)));
+                s[j][2] = rcp(1.f + ex2(-fmaf(s[j][2], scale_log2, bias1)));
+                s[j][3] = rcp(1.f + ex2(-fmaf(s[j][3], scale_log2, bias1)));
             }
         }
     } else {

@@ -176,6 +176,12 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// 1 / x in float (the hardware's approximation, 1 ulp); 1 / inf = 0
+__device__ __forceinline__ float rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 // Byte offset of 16-byte chunk ``c`` (0 .. D/8 - 1) of row ``r`` in a tile made of [rows x 64] swizzled blocks.
 __device__ __forceinline__ int swizzled(int r, int c, int block_bytes) {
     return (c >> 3) * block_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
@@ -243,7 +249,7 @@ __device__ __forceinline__ void row_sigmoid(const unsigned* r, unsigned p_addr, 
         for (int i = 0; i < 16; ++i) {
             const int k = c + 2 * i;
             const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), scale2, bias2);
-            float2 e = make_float2(__frcp_rn(1.f + ex2(t.x)), __frcp_rn(1.f + ex2(t.y)));
+            float2 e = make_float2(rcp(1.f + ex2(t.x)), rcp(1.f + ex2(t.y)));
             if (MASKED) {
                 if (k > hi || k < lo) e.x = 0.f;
                 if (k + 1 > hi || k + 1 < lo) e.y = 0.f;

@@ -80,7 +80,7 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
                 group_kept[g] = 0.f;
             }
             __syncwarp();
-            for (int round = 0; round < keep; ++round) {
+            for (int pick = 0; pick < keep; ++pick) {
                 float best = -CUDART_INF_F;
                 int at = groups;
                 for (int g = lane; g < groups; g += 32)
