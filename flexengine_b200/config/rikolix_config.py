@@ -115,9 +115,9 @@ class RikolixConfig:
                     origin = parsed[j].mixer if 0 <= j < i else None
                     if not isinstance(origin, LatentMixerConfig) or origin.kv_from is not None:
                         raise ConfigError(f"layer {i}: kv_from must name an earlier latent_attention layer that makes its own latents")
-                    if (origin.kv_rank, origin.rot_dim, origin.rot_base, origin.rot_dims) != \
-                            (mixer.kv_rank, mixer.rot_dim, mixer.rot_base, mixer.rot_dims):
-                        raise ConfigError(f"layer {i}: kv_rank, rot_dim and rotation must equal those of layer {j}, whose latents it reads")
+                    # the cached rows are the maker's: their layout has to fit; the reader's queries turn by its own rotation
+                    if (origin.kv_rank, origin.rot_dim) != (mixer.kv_rank, mixer.rot_dim):
+                        raise ConfigError(f"layer {i}: kv_rank and rot_dim must equal those of layer {j}, whose latents it reads")
             else:
                 raise ConfigError(f"layer {i}: unknown mixer type {kind!r}; known: {', '.join(MIXERS)}")
             mlp_data = entry.get("mlp")

@@ -182,6 +182,7 @@ def test_configuration_errors_are_named():
         (lambda c: c["layers"][1]["mixer"].update(kv_from=1), "kv_from"),
         (lambda c: c["layers"][3]["mixer"].update(kv_from=1), "kv_from"),
         (lambda c: c["layers"][1]["mixer"].update(kv_rank=24), "kv_rank"),
+        (lambda c: c["layers"][3]["mixer"].update(rot_dim=8), "rot_dim"),
         (lambda c: c["layers"][2]["mixer"].update(kv_heads=3), "kv_heads"),
         (lambda c: c["layers"][2]["mixer"]["rot"].update(dims=7), "rot.dims"),
         (lambda c: c["layers"][2]["mixer"].update(vdim=13), "vdim"),
@@ -267,7 +268,8 @@ def attention_part(D, m, weights, device, dt, eps=1e-5):
 
 # heads, kv_heads, dim, vdim, rotated entries: values wider and narrower than keys, one head, groups of one, two and four, no
 # rotation, part of a head and a whole head, head size 64 and 128 (tensor-core kernels in bfloat16)
-ATTENTION_SHAPES = [(4, 2, 16, 24, 8), (2, 1, 32, 16, 32), (3, 3, 16, 16, 0), (8, 2, 64, 64, 16), (1, 1, 40, 8, 2), (6, 3, 64, 128, 64)]
+ATTENTION_SHAPES = [(4, 2, 16, 24, 8), (2, 1, 32, 16, 32), (3, 3, 16, 16, 0), (8, 2, 64, 64, 16), (1, 1, 40, 8, 2), (6, 3, 64, 128, 64),
+                    (2, 1, 8, 32, 4), (8, 4, 16, 8, 8), (2, 1, 24, 64, 24), (12, 3, 128, 24, 2), (12, 4, 24, 64, 12)]
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
@@ -347,7 +349,7 @@ def latent_part(D, m, weights, device, dt, shared=False, eps=1e-5):
 # heads, dim, rot_dim, vdim, kv_rank, q_rank: rows that need padding and rows that do not, one head, part of the rotated part
 # turned, rows of 64 and 128 (tensor-core kernels in bfloat16) and of 272 (beyond them)
 LATENT_SHAPES = [(3, 8, 4, 12, 20, 10, None), (2, 24, 8, 24, 40, 32, 4), (1, 12, 2, 20, 24, 16, None), (4, 32, 16, 32, 48, 24, None),
-                 (6, 32, 16, 32, 112, 96, None), (2, 16, 16, 16, 256, 8, 8)]
+                 (6, 32, 16, 32, 112, 96, None), (2, 16, 16, 16, 256, 8, 8), (2, 4, 32, 12, 12, 4, 16), (4, 64, 8, 4, 112, 24, None)]
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
