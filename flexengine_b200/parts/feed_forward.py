@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: down( act(gate(h)) * up(h) ), act = silu (SwiGLU) or the tanh form of GELU.
+"""Feed-forwards: the dense gated one, down( act(gate(h)) * up(h) ), act = silu (SwiGLU) or the tanh form of GELU; the dense
+one without a gate, down( act(up(h)) ), act = xIELU or the square of relu; and the routed one (a mixture of experts of either form).
 
 Formula: tests/unit/test_synthetic_qwen.py:30-36 of the reference (its product code
 calls the module opaquely, src/flexengine/inference/models/qwen2.py:130).  gate and up
